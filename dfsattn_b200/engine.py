@@ -1,0 +1,206 @@
+"""Host logic shared by the HunyuanVideo and Wan DFS attention operators.
+
+Device-resident pieces built once and reused: the int32 permutation and its
+inverse (the reference rebuilds and re-uploads them on every call,
+dfsattn/attention_hyvideo.py:1116-1120), the scoring workspace, and the
+per-layer block index lists (the reference caches bool masks,
+attention_hyvideo.py:1165-1183).
+"""
+import math
+from dataclasses import dataclass
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import ops
+
+BLOCK = ops.BLOCK
+
+
+@dataclass
+class BlockLists:
+    """Selected key blocks per (head, query block): ascending lists."""
+    idx: torch.Tensor  # int32 [H, Qb, kmax], -1 padded
+    cnt: torch.Tensor  # int32 [H, Qb]
+    k_blocks: int
+
+    def clone(self) -> "BlockLists":
+        return BlockLists(self.idx.clone(), self.cnt.clone(), self.k_blocks)
+
+    def to_bool_mask(self) -> torch.Tensor:
+        """bool [H, Qb, Kb] (the reference's mask format)."""
+        H, Qb, kmax = self.idx.shape
+        mask = torch.zeros((H, Qb, self.k_blocks + 1), dtype=torch.bool, device=self.idx.device)
+        safe = torch.where(self.idx >= 0, self.idx, torch.full_like(self.idx, self.k_blocks)).long()
+        mask.scatter_(-1, safe, True)
+        return mask[..., : self.k_blocks]
+
+    @staticmethod
+    def from_bool_mask(mask: torch.Tensor) -> "BlockLists":
+        H, Qb, Kb = mask.shape
+        cnt = mask.sum(dim=-1).to(torch.int32)
+        kmax = max(int(cnt.max().item()), 1)
+        order = torch.argsort((~mask).to(torch.int8), dim=-1, stable=True)[..., :kmax].to(torch.int32)
+        pos = torch.arange(kmax, device=mask.device)[None, None, :]
+        idx = torch.where(pos < cnt[..., None], order, torch.full_like(order, -1))
+        return BlockLists(idx.contiguous(), cnt.contiguous(), Kb)
+
+
+class PermutationCache:
+    """int32 (perm, inverse) on the device, keyed by the permutation's identity."""
+
+    def __init__(self):
+        self._cache: Dict[tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+    def get(self, video_perm: Optional[torch.Tensor], seq_len: int, video_len: int,
+            device: torch.device) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+        if video_perm is None:
+            return None, None  # raster order: no gather at all
+        key = (video_perm.data_ptr(), int(video_perm.numel()), int(video_perm._version), seq_len,
+               video_len, str(device))
+        hit = self._cache.get(key)
+        if hit is not None:
+            return hit
+        if video_perm.numel() != video_len:
+            raise ValueError(f"video_perm has {video_perm.numel()} entries, expected video_len={video_len}")
+        if seq_len >= 2 ** 31:
+            raise ValueError("sequence too long for int32 token indices")
+        vp = video_perm.to(device=device, dtype=torch.int64)
+        if seq_len > video_len:  # text tokens stay in place at the tail
+            perm = torch.cat([vp, torch.arange(video_len, seq_len, device=device, dtype=torch.int64)])
+        else:
+            perm = vp
+        inv = torch.empty_like(perm)
+        inv[perm] = torch.arange(seq_len, device=device, dtype=torch.int64)
+        out = (perm.to(torch.int32).contiguous(), inv.to(torch.int32).contiguous())
+        self._cache[key] = out
+        return out
+
+    def clear(self):
+        self._cache.clear()
+
+
+_perm_cache = PermutationCache()
+_workspaces: Dict[str, torch.Tensor] = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    key = str(device)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def clear_device_caches():
+    _perm_cache.clear()
+    _workspaces.clear()
+
+
+def topk_block_num(sparsity: float, k_blocks: int) -> int:
+    """max(1, int(s * Kb)) in float64, as dfsattn/attention_hyvideo.py:432."""
+    return max(1, int(float(sparsity) * k_blocks))
+
+
+def select_lists(scores: torch.Tensor, seq_len: int, video_len: int, sparsity: float,
+                 flavor: str, want_mask: bool = False):
+    """Index lists from fp32 block scores with the reference's budget rules.
+
+    flavor "hyvideo": dfsattn/attention_hyvideo.py:424-443,491-501 (text and
+    boundary key blocks use up budget and are always on; rows from the first
+    block holding a text token on are dense).  flavor "wan":
+    dfsattn/attention_wan.py:248-253 (plain top-k over every key block).
+    """
+    kb = math.ceil(seq_len / BLOCK)
+    kk = topk_block_num(sparsity, kb)
+    if flavor == "wan":
+        return ops.select_topk(scores, q_rows=kb, n_rank=kb, k_select=kk, dense_row_start=kb,
+                               want_mask=want_mask)
+    dense_start = video_len // BLOCK
+    n_text_blocks = max(0, kb - dense_start)
+    text_len = seq_len - video_len
+    if n_text_blocks > 0:
+        n_sel = kk - n_text_blocks
+        if n_sel <= 0:
+            raise AssertionError("num_video_blocks_to_select must be non-negative")
+        n_rank = dense_start
+    else:
+        n_sel, n_rank = kk, kb
+    dense_row_start = dense_start if text_len > 0 else kb
+    return ops.select_topk(scores, q_rows=kb, n_rank=n_rank, k_select=n_sel,
+                           dense_row_start=dense_row_start, want_mask=want_mask)
+
+
+def compute_block_lists(q_perm, k_perm, video_len: int, sparsity: float, flavor: str,
+                        tile: int = ops.TILE) -> BlockLists:
+    """Scores + selection on permuted [H, L, D] tensors -> BlockLists."""
+    H, L, D = q_perm.shape
+    wan = flavor == "wan"
+    need = ops.lib.dfs_score_workspace_bytes(H, L, L if wan else video_len, D, tile, BLOCK, int(wan))
+    if need < 0:
+        ops.check(int(need), "dfs_score_workspace_bytes")
+    scores = ops.block_scores(q_perm, k_perm, L if wan else video_len, wan, tile=tile,
+                              workspace=_workspace(q_perm.device, int(need)))
+    idx, cnt, _ = select_lists(scores, L, L if wan else video_len, sparsity, flavor)
+    return BlockLists(idx, cnt, math.ceil(L / BLOCK))
+
+
+def _as_heads(x: torch.Tensor) -> torch.Tensor:
+    if x.dim() != 4 or x.shape[0] != 1:
+        raise AssertionError("DFS Attention with block sparse currently supports batch size 1.")
+    return x[0]
+
+
+def prepare_inputs(q, k, v):
+    """[1,H,L,D] (any float dtype, CUDA) -> contiguous bf16 [H,L,D] views/copies."""
+    outs = []
+    for t in (q, k, v):
+        t = _as_heads(t)
+        if not t.is_cuda:
+            raise ValueError("dfsattn_b200 runs on CUDA tensors only (no CPU fallback)")
+        if t.dtype != torch.bfloat16:
+            t = t.to(torch.bfloat16)
+        outs.append(t.contiguous())
+    return outs
+
+
+def valid_length(cu_seqlens, seq_len: int) -> int:
+    """End of the first varlen segment from cu_seqlens = [0, valid, L]
+    (dfsattn/replace_hyvideo.py:221-228); None means one segment."""
+    if cu_seqlens is None:
+        return seq_len
+    vals = cu_seqlens.tolist() if isinstance(cu_seqlens, torch.Tensor) else list(cu_seqlens)
+    if len(vals) < 2:
+        return seq_len
+    valid = int(vals[1])
+    return seq_len if valid <= 0 or valid > seq_len else valid
+
+
+def run_attention(qp, kp, vp, lists: Optional[BlockLists], perm_i32, valid_len: int) -> torch.Tensor:
+    """Block-sparse (or dense when ``lists`` is None) attention on permuted
+    bf16 [H,L,D]; returns the un-permuted result [H,L,D].
+
+    A padded tail [valid_len, L) forms a second, independent varlen segment
+    whose block coordinates restart at zero (block_sparse_attn semantics,
+    dfsattn/attention_hyvideo.py:1055,1075-1082); it is a second launch on the
+    tail rows with the top-left corner of the same block mask.
+    """
+    H, L, D = qp.shape
+    idx = lists.idx if lists is not None else None
+    cnt = lists.cnt if lists is not None else None
+    out = ops.block_sparse_fwd(qp, kp, vp, idx, cnt, out_row_map=perm_i32, kv_len=valid_len)
+    if valid_len < L:
+        tail = L - valid_len
+        if perm_i32 is not None and not bool((perm_i32[valid_len:] == torch.arange(
+                valid_len, L, device=qp.device, dtype=torch.int32)).all()):
+            raise ValueError("the padded tail must lie in the un-permuted (text) part of the sequence")
+        q2, k2, v2 = (t[:, valid_len:].contiguous() for t in (qp, kp, vp))
+        lists2 = None
+        if lists is not None:
+            nb2 = math.ceil(tail / BLOCK)
+            lists2 = BlockLists.from_bool_mask(lists.to_bool_mask()[:, :nb2, :nb2].contiguous())
+        o2 = ops.block_sparse_fwd(q2, k2, v2, None if lists2 is None else lists2.idx,
+                                  None if lists2 is None else lists2.cnt, kv_len=tail)
+        out[:, valid_len:] = o2
+    return out

@@ -1,0 +1,180 @@
+"""Torch-facing wrappers over the C ABI (include/dfs_b200.h).
+
+Torch is used only for device memory and the current stream; every operator
+below is one call into libdfs_b200.so.  Tensors are head-major [H, L, D].
+"""
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+
+BLOCK = 128
+TILE = 16
+
+_DTYPE_CODE = {torch.bfloat16: 0, torch.float32: 1}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("dfsattn_b200 operators need CUDA tensors (there is no CPU path)")
+
+
+# ---- status word ------------------------------------------------------------
+_status = {}
+
+
+def status_tensor(device) -> torch.Tensor:
+    """Per-device int32 word that kernels set when a bounded wait expired."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device=None):
+    """Synchronise and raise if any kernel on ``device`` reported a give-up."""
+    device = torch.device("cuda" if device is None else device)
+    word = status_tensor(device)
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise RuntimeError(f"dfsattn_b200 kernel reported device status {code} (bounded wait expired)")
+
+
+# ---- host helpers -------------------------------------------------------------
+def hilbert3d_perm(f: int, h: int, w: int) -> torch.Tensor:
+    out = torch.empty(f * h * w, dtype=torch.int64)
+    check(lib.dfs_hilbert3d_perm(f, h, w, out.data_ptr()), "dfs_hilbert3d_perm")
+    return out
+
+
+def cache_schedule(step_idx, skip_steps, cache_interval, sparsity, sparsity_dcrt) -> Tuple[bool, float]:
+    import ctypes
+    flag, cur = ctypes.c_int(0), ctypes.c_double(0.0)
+    rc = lib.dfs_cache_schedule(int(step_idx), int(skip_steps), int(cache_interval), float(sparsity),
+                                float(sparsity_dcrt), ctypes.byref(flag), ctypes.byref(cur))
+    if rc == -5:  # DFS_ERR_RANGE: the reference raises ValueError here
+        raise ValueError("cache_interval must be greater than 0.")
+    check(rc, "dfs_cache_schedule")
+    return bool(flag.value), float(cur.value)
+
+
+def interaction_count(idx: Optional[torch.Tensor], cnt: Optional[torch.Tensor], heads, seq_len,
+                      block=BLOCK) -> int:
+    qb = kb = math.ceil(seq_len / block)
+    if idx is None:
+        r = lib.dfs_interaction_count(None, None, heads, qb, kb, 0, seq_len, block)
+    else:
+        idx_h = idx.detach().to("cpu", torch.int32).contiguous()
+        cnt_h = cnt.detach().to("cpu", torch.int32).contiguous()
+        r = lib.dfs_interaction_count(idx_h.data_ptr(), cnt_h.data_ptr(), heads, qb, kb, idx_h.shape[-1],
+                                      seq_len, block)
+    if r < 0:
+        check(int(r), "dfs_interaction_count")
+    return int(r)
+
+
+# ---- permutation ----------------------------------------------------------------
+def permute_qkv(q, k, v, perm_i32):
+    """Gather rows of three [H, L, D] tensors by ``perm_i32`` in one launch."""
+    _need_cuda(q, k, v, perm_i32)
+    outs = [torch.empty_like(t) if t is not None else None for t in (q, k, v)]
+    first = next(t for t in (q, k, v) if t is not None)
+    H, L, D = first.shape
+    for t in (q, k, v):
+        if t is not None and (not t.is_contiguous() or t.shape != first.shape or t.dtype != first.dtype):
+            raise ValueError("q, k, v must be contiguous [H, L, D] tensors of one dtype")
+    check(lib.dfs_permute_qkv(_ptr(q), _ptr(k), _ptr(v), perm_i32.data_ptr(), _ptr(outs[0]), _ptr(outs[1]),
+                              _ptr(outs[2]), H, L, D * first.element_size(), _stream(first.device)),
+          "dfs_permute_qkv")
+    return tuple(outs)
+
+
+def unpermute(x, inv_perm_i32):
+    _need_cuda(x, inv_perm_i32)
+    if not x.is_contiguous():
+        raise ValueError("x must be contiguous [H, L, D]")
+    H, L, D = x.shape
+    out = torch.empty_like(x)
+    check(lib.dfs_unpermute(x.data_ptr(), inv_perm_i32.data_ptr(), out.data_ptr(), H, L,
+                            D * x.element_size(), _stream(x.device)), "dfs_unpermute")
+    return out
+
+
+# ---- scoring + selection ----------------------------------------------------------
+def block_scores(q_perm, k_perm, video_len: int, wan_layout: bool, tile=TILE, block=BLOCK,
+                 workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 block scores [H, Rb, Kb] from permuted [H, L, D] tensors."""
+    _need_cuda(q_perm, k_perm)
+    if q_perm.dtype not in _DTYPE_CODE or k_perm.dtype != q_perm.dtype:
+        raise ValueError("scores need bf16 or fp32 inputs")
+    if not (q_perm.is_contiguous() and k_perm.is_contiguous()):
+        raise ValueError("q, k must be contiguous")
+    H, L, D = q_perm.shape
+    need = lib.dfs_score_workspace_bytes(H, L, video_len, D, tile, block, int(wan_layout))
+    if need < 0:
+        check(int(need), "dfs_score_workspace_bytes")
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q_perm.device)
+    kb = math.ceil(L / block)
+    rb = kb if wan_layout else math.ceil(video_len / block)
+    out = torch.empty((H, rb, kb), dtype=torch.float32, device=q_perm.device)
+    check(lib.dfs_block_scores(q_perm.data_ptr(), k_perm.data_ptr(), _DTYPE_CODE[q_perm.dtype], H, L,
+                               video_len, D, tile, block, int(wan_layout), out.data_ptr(),
+                               workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+                               _stream(q_perm.device)), "dfs_block_scores")
+    return out
+
+
+def select_topk(scores, q_rows: int, n_rank: int, k_select: int, dense_row_start: int,
+                want_mask: bool = False):
+    """Index lists (idx int32 [H, q_rows, kmax], cnt int32 [H, q_rows]) from fp32
+    block scores [H, score_rows, n_cols]; optional uint8 mask [H, q_rows, n_cols]."""
+    _need_cuda(scores)
+    if scores.dtype != torch.float32 or not scores.is_contiguous():
+        raise ValueError("scores must be contiguous fp32")
+    H, score_rows, n_cols = scores.shape
+    sparse_cnt = k_select + (n_cols - n_rank)
+    kmax = n_cols if dense_row_start < q_rows else sparse_cnt
+    idx = torch.empty((H, q_rows, kmax), dtype=torch.int32, device=scores.device)
+    cnt = torch.empty((H, q_rows), dtype=torch.int32, device=scores.device)
+    mask = torch.empty((H, q_rows, n_cols), dtype=torch.uint8, device=scores.device) if want_mask else None
+    check(lib.dfs_select_topk(scores.data_ptr(), H, score_rows, q_rows, n_cols, n_rank, k_select,
+                              dense_row_start, idx.data_ptr(), cnt.data_ptr(), kmax, _ptr(mask),
+                              _stream(scores.device)), "dfs_select_topk")
+    return idx, cnt, mask
+
+
+# ---- attention -----------------------------------------------------------------------
+def block_sparse_fwd(q_perm, k_perm, v_perm, idx, cnt, out_row_map=None, kv_len=None, scale=None,
+                     out=None):
+    """bf16 block-sparse attention over permuted [H, L, D] tensors; ``idx=None``
+    attends every key block (dense)."""
+    _need_cuda(q_perm, k_perm, v_perm)
+    for t in (q_perm, k_perm, v_perm):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.shape != q_perm.shape:
+            raise ValueError("q, k, v must be contiguous bf16 [H, L, D] tensors of one shape")
+    H, L, D = q_perm.shape
+    if out is None:
+        out = torch.empty_like(q_perm)
+    kv_len = L if kv_len is None else int(kv_len)
+    scale = D ** -0.5 if scale is None else float(scale)
+    kmax = 0 if idx is None else idx.shape[-1]
+    check(lib.dfs_block_sparse_fwd(q_perm.data_ptr(), k_perm.data_ptr(), v_perm.data_ptr(), _ptr(idx),
+                                   _ptr(cnt), kmax, _ptr(out_row_map), out.data_ptr(), H, L, kv_len, D,
+                                   scale, status_tensor(q_perm.device).data_ptr(),
+                                   _stream(q_perm.device)), "dfs_block_sparse_fwd")
+    return out

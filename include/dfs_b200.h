@@ -1,0 +1,149 @@
+/*
+ * dfs_b200.h -- C ABI of the B200 (sm_100a) DFS sparse-attention kernels.
+ *
+ * Drop-in boundary for the native DFS attention path of codesiena/DFSattn:
+ * Hilbert permute -> pooled block scoring -> per-row top-k block selection ->
+ * 128x128 block-sparse attention -> inverse permute.  The reference performs
+ * these steps with PyTorch ops and a third-party CUDA extension; a binding
+ * (ctypes / pybind / cffi) replaces those calls with the entry points below.
+ * Citations are paths inside the reference repository.
+ *
+ * Conventions
+ *  - Every function returns an int status: 0 = ok, negative = rejected
+ *    argument (nothing was launched), positive = CUDA runtime error code.
+ *  - Unless stated otherwise pointers are DEVICE pointers; tensors are dense,
+ *    row-major, "head-major" [H, L, D] (the reference's [1,H,L,D] with the
+ *    batch of one dropped; attention_hyvideo.py:399 asserts batch 1).
+ *  - `stream` is a cudaStream_t passed as void*.  No call synchronises, none
+ *    allocates device memory, none keeps global state.
+ *  - Kernels never trap: every wait inside a kernel is bounded; a kernel that
+ *    gives up writes a non-zero code to `*status` (device int32, caller
+ *    zero-initialised, may be NULL for kernels that have no waits).
+ */
+#ifndef DFS_B200_H
+#define DFS_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DFS_B200_VERSION 1
+
+/* element types of Q/K/V/O */
+#define DFS_DTYPE_BF16 0
+#define DFS_DTYPE_F32 1
+
+/* argument-rejection codes (negative return values) */
+#define DFS_ERR_NULL -1        /* required pointer is NULL                   */
+#define DFS_ERR_ALIGN -2       /* pointer not 16-byte aligned                */
+#define DFS_ERR_SHAPE -3       /* unsupported shape (D, block, tile, sizes)  */
+#define DFS_ERR_DTYPE -4       /* unsupported element type                   */
+#define DFS_ERR_RANGE -5       /* k / count / length out of range            */
+#define DFS_ERR_WORKSPACE -6   /* workspace too small                        */
+#define DFS_ERR_DRIVER -7      /* tensor-map encode entry point unavailable  */
+
+/* device status codes written by kernels to *status */
+#define DFS_STATUS_OK 0
+#define DFS_STATUS_WAIT_TIMEOUT 1 /* a bounded barrier wait expired           */
+
+int dfs_version(void);
+const char* dfs_status_string(int code);
+
+/* ---- host-side helpers (no GPU needed) --------------------------------- */
+
+/* 3-D Hilbert token order over an f x h x w latent grid.
+ * Replaces hilbert3d_perm(), dfsattn/utils/order.py:206-258 (curve over the
+ * enclosing 2^b cube, points outside the grid dropped; coordinates ordered
+ * [x, y, z]; raster index z*h*w + y*w + x).  perm_out: HOST int64[f*h*w]. */
+int dfs_hilbert3d_perm(int f, int h, int w, int64_t* perm_out);
+
+/* Refresh flag and current sparsity for a denoising step.
+ * Replaces _compute_cache_schedule(), dfsattn/attention_hyvideo.py:40-65.
+ * Returns DFS_ERR_RANGE when cache_interval <= 0 (the reference raises). */
+int dfs_cache_schedule(int step_idx, int skip_steps, int cache_interval, double sparsity,
+                       double sparsity_dcrt, int* is_cache_step, double* current_sparsity);
+
+/* Selected (q,k) token pairs of index lists, with partial last blocks.
+ * Replaces _block_interaction_count(), dfsattn/attention_hyvideo.py:521-546.
+ * idx/cnt are HOST copies of the lists (idx may be NULL for "all blocks"). */
+int64_t dfs_interaction_count(const int32_t* idx_host, const int32_t* cnt_host, int heads,
+                              int q_blocks, int k_blocks, int kmax, int64_t seq_len, int block);
+
+/* ---- permutation -------------------------------------------------------- */
+
+/* dst[h, i, :] = src[h, perm[i], :] for three tensors in one launch.
+ * Replaces _apply_permutation_in_place() x3, dfsattn/attention_hyvideo.py:177-184
+ * as called at :1034-1036.  row_bytes = D * sizeof(element), multiple of 16.
+ * Any of the three (src,dst) pairs may be NULL/NULL to skip it. */
+int dfs_permute_qkv(const void* q, const void* k, const void* v, const int32_t* perm,
+                    void* q_out, void* k_out, void* v_out, int heads, int64_t seq_len,
+                    int row_bytes, void* stream);
+
+/* dst[h, i, :] = src[h, inv_perm[i], :].
+ * Replaces _apply_inverse_permutation(), dfsattn/attention_hyvideo.py:187-194
+ * (call site :1086).  The attention entry point can write un-permuted rows
+ * itself (out_row_map), which makes this call unnecessary on the hot path. */
+int dfs_unpermute(const void* src, const int32_t* inv_perm, void* dst, int heads,
+                  int64_t seq_len, int row_bytes, void* stream);
+
+/* ---- scoring + selection ------------------------------------------------ */
+
+/* Bytes of scratch dfs_block_scores needs for this shape. */
+int64_t dfs_score_workspace_bytes(int heads, int64_t seq_len, int64_t video_len, int head_dim,
+                                  int tile, int block, int wan_layout);
+
+/* Pooled block scores, fp32 [H, Rb, Kb] with Kb = ceil(L/block) and
+ * Rb = ceil(video_len/block) (hyvideo layout) or Kb (wan layout).
+ * Replaces _compute_tile_score() + the 8x8 tile sums,
+ * dfsattn/attention_hyvideo.py:310-385,419-422 (hyvideo layout: zero gap
+ * between video and text, query tiles cover the video part only) and
+ * dfsattn/attention_wan.py:157-209,243-246 (wan_layout != 0: zero pad at the
+ * end only, query tiles cover everything).  q, k are the PERMUTED tensors
+ * [H, L, D] (bf16 or f32); means, logits and softmax are computed in fp32.
+ * tile must be 16 and block 128. */
+int dfs_block_scores(const void* q_perm, const void* k_perm, int dtype, int heads,
+                     int64_t seq_len, int64_t video_len, int head_dim, int tile, int block,
+                     int wan_layout, float* block_scores, void* workspace,
+                     int64_t workspace_bytes, void* stream);
+
+/* Per (head, row): the k_select largest of scores[h, r, 0:n_rank) (ties: lowest
+ * column first), plus every column in [n_rank, n_cols) ("forced" columns),
+ * written in ascending order to idx[h, r, 0:cnt) and padded with -1 up to
+ * kmax; rows r >= dense_row_start select every column.
+ * Replaces torch.topk + scatter_ and the dense text rules,
+ * dfsattn/attention_hyvideo.py:431-443,491-501 and attention_wan.py:248-253.
+ * scores: fp32 [H, score_rows, n_cols]; idx: int32 [H, q_rows, kmax];
+ * cnt: int32 [H, q_rows]; mask_out (optional): uint8 [H, q_rows, n_cols].
+ * Rows r >= score_rows must be dense rows. */
+int dfs_select_topk(const float* scores, int heads, int score_rows, int q_rows, int n_cols,
+                    int n_rank, int k_select, int dense_row_start, int32_t* idx, int32_t* cnt,
+                    int kmax, uint8_t* mask_out, void* stream);
+
+/* ---- block-sparse attention forward ------------------------------------- */
+
+/* O[h, map(i), :] = softmax_j( q_i . k_j * scale ) v_j over the keys j of the
+ * 128-token key blocks listed for query block i/128, bf16 in / fp32
+ * accumulate / bf16 out, on tcgen05 tensor cores.
+ * Replaces block_sparse_attn_func(..., base_blockmask, ...) as called at
+ * dfsattn/attention_hyvideo.py:1075-1082 and attention_wan.py:379-386, and,
+ * with idx == NULL (every key block), flash_attn_varlen_func at
+ * dfsattn/fullattention.py:108-116.
+ *  q, k, v : bf16 [H, L, D], already permuted; D = 64 or 128.
+ *  idx/cnt : int32 [H, Qb, kmax] / [H, Qb] ascending block lists (Qb = ceil(L/128)).
+ *  kv_len  : keys j >= kv_len are masked out (L when there is no padding).
+ *  out_row_map : int32 [L] or NULL; row i of the result is stored at row
+ *            out_row_map[i] (pass the forward permutation to fuse the
+ *            inverse permute of attention_hyvideo.py:1086).
+ *  scale   : softmax scale (the reference uses D^-0.5).
+ *  status  : device int32, zero-initialised by the caller. */
+int dfs_block_sparse_fwd(const void* q, const void* k, const void* v, const int32_t* idx,
+                         const int32_t* cnt, int kmax, const int32_t* out_row_map, void* out,
+                         int heads, int64_t seq_len, int64_t kv_len, int head_dim, float scale,
+                         int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DFS_B200_H */
