@@ -309,7 +309,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after_sync();
       const long long tok = static_cast<long long>(qb) * kBlockM + row;
       const float inv_l = l_sum > 0.f ? 1.0f / l_sum : 0.f;
-      const bool live = tok < p.seq_len && n_tiles > 0;
+      const bool live = tok < p.seq_len;  // a row with an empty list gets zeros
       long long dst_row = tok;
       if (live && p.out_row_map) dst_row = __ldg(p.out_row_map + tok);
       __nv_bfloat16* dst = p.out + (static_cast<size_t>(head) * p.seq_len + (live ? dst_row : 0)) * HD;
@@ -320,6 +320,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (n_tiles > 0) {
           tmem_ld32(o_addr + g * 32, o);
           tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
         }
         if (dump) {
 #pragma unroll

@@ -1,0 +1,94 @@
+"""CPU: the C-ABI library loads, exports every symbol the header declares, and
+its host-only entry points (no GPU needed) agree with the oracle."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from dfsattn_b200 import _lib
+    header = open(os.path.join(ROOT, "include", "dfs_b200.h")).read()
+    declared = set(re.findall(r"\b(dfs_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(_lib.SIGNATURES), (declared ^ set(_lib.SIGNATURES))
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared:
+        assert hasattr(raw, name), name
+    assert _lib.lib.dfs_version() == 1
+    assert b"aligned" in _lib.lib.dfs_status_string(-2)
+
+
+def test_missing_library_fails_loudly(tmp_path, monkeypatch):
+    from dfsattn_b200 import _lib
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(_lib.DfsLibraryError):
+        _lib._load()
+
+
+def test_schedule_entry_point_matches_reference_tables(golden_dir):
+    from dfsattn_b200.attention_hyvideo import _compute_cache_schedule
+    g = np.load(golden_dir + "/schedule.npz")
+    i = 0
+    while f"params_{i}" in g:
+        skip, interval, s, dcrt, steps = g[f"params_{i}"]
+        for step in range(int(steps)):
+            flag, val = _compute_cache_schedule(step, int(skip), int(interval), float(s), float(dcrt))
+            assert flag == bool(g[f"flags_{i}"][step]) and val == float(g[f"vals_{i}"][step])
+        i += 1
+    with pytest.raises(ValueError):
+        _compute_cache_schedule(0, 0, 0, 0.3, 0.1)
+
+
+def test_interaction_count_entry_point_handles_partial_edges():
+    # reference analogue: tests/test_flashinfer64_attention.py:95-120
+    from dfsattn_b200 import ops
+    torch.manual_seed(38)
+    for L in (193, 256, 1191):
+        kb = -(-L // 128)
+        mask = torch.rand(2, kb, kb) > 0.5
+        idx, cnt = oracle.mask_to_index_lists(mask)
+        if idx.shape[-1] == 0:
+            continue
+        assert ops.interaction_count(idx, cnt, 2, L) == oracle.block_interaction_count(mask, L)
+        assert ops.interaction_count(None, None, 2, L) == 2 * L * L
+
+
+def test_cpu_tensors_are_rejected_not_computed():
+    from dfsattn_b200 import ops
+    x = torch.zeros(1, 128, 128, dtype=torch.bfloat16)
+    p = torch.arange(128, dtype=torch.int32)
+    with pytest.raises(ValueError):
+        ops.permute_qkv(x, x, x, p)
+    with pytest.raises(ValueError):
+        ops.block_scores(x, x, 128, True)
+    with pytest.raises(ValueError):
+        ops.block_sparse_fwd(x, x, x, None, None)
+
+
+def test_processor_constructors_keep_the_reference_argument_order():
+    from dfsattn_b200.replace_hyvideo import HunyuanVideo_DFSAttn_Processor2_0 as HP
+    from dfsattn_b200.replace_wan import Wan_DFSAttn_Processor2_0 as WP
+    hp = HP("dfs", 0.3, 16, 128, 1024, None, 5, [0], 12, 12, 0.1, True)
+    assert (hp.layer_idx, hp.video_len, hp.skip_steps, hp.cache_flag, hp.step_idx) == (5, 1024, 12, True, 0)
+    wp = WP("dfs", 0.3, 16, 128, None, 4, [0], 12, 12, 0.1, True, False)
+    assert (wp.layer_idx, wp.cross_flag, wp.dense_step_idx) == (4, False, -1)
+    # the gate follows step and layer
+    hp.step_idx = 11
+    assert not hp._is_sparse_call()
+    hp.step_idx = 12
+    assert hp._is_sparse_call()
+    hp.skip_layers = [5]
+    assert not hp._is_sparse_call()
+    for bad in (dict(sparse_execution="flashinfer64"), dict(selector_mode="kp"), dict(token_top_k=8)):
+        with pytest.raises(ValueError):
+            HP("dfs", 0.3, 16, 128, 1024, None, 5, [0], 12, 12, 0.1, True, **bad)
+    with pytest.raises(ValueError):
+        HP("dfs", 0.3, 32, 128, 1024, None, 5, [0], 12, 12, 0.1, True)
