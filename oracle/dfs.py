@@ -223,7 +223,7 @@ def mask_to_index_lists(mask):
 # --------------------------------------------------------------------------- #
 # attention
 # --------------------------------------------------------------------------- #
-def block_sparse_attention(q, k, v, perm, inv_perm, mask, block=128, valid_len=None):
+def block_sparse_attention(q, k, v, perm, inv_perm, mask, block=128, valid_len=None, q_block_range=None):
     """Block-sparse attention in the permuted order, un-permuted on return.
 
     Semantics of the native branch, dfsattn/attention_hyvideo.py:1034-1086:
@@ -235,6 +235,8 @@ def block_sparse_attention(q, k, v, perm, inv_perm, mask, block=128, valid_len=N
 
     ``valid_len``: end of the first varlen segment (cu_seqlens [0, valid, L],
     dfsattn/replace_hyvideo.py:221-228); None means one segment.
+    ``q_block_range``: (first, last+1) query blocks to compute (timing samples);
+    rows outside stay zero.
     """
     b, h, L, d = q.shape
     assert b == 1
@@ -247,6 +249,8 @@ def block_sparse_attention(q, k, v, perm, inv_perm, mask, block=128, valid_len=N
     for s0, s1 in segs:
         n = s1 - s0
         for qb in range(math.ceil(n / block)):
+            if q_block_range is not None and not (q_block_range[0] <= qb < q_block_range[1]):
+                continue
             r0, r1 = s0 + qb * block, min(s0 + (qb + 1) * block, s1)
             for hh in range(h):
                 cols = torch.nonzero(mask[hh, qb, : math.ceil(n / block)]).flatten().tolist()
