@@ -1,6 +1,9 @@
 """Build the C-ABI shared library (sm_100a only) in-tree with nvcc.
 
-    python -m dfsattn_b200.build          # -> dfsattn_b200/libdfs_b200.so
+    python dfsattn_b200/build.py          # -> dfsattn_b200/libdfs_b200.so
+
+Run it as a script (or load it by path): importing the package first would
+try to load the library that is being built.
 """
 import os
 import shutil
