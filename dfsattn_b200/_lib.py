@@ -26,6 +26,9 @@ SIGNATURES = {
     "dfs_score_workspace_bytes": (c_int64, [c_int, c_int64, c_int64, c_int, c_int, c_int, c_int]),
     "dfs_block_scores": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int,
                                  c_int, c_void_p, c_void_p, c_int64, c_void_p]),
+    "dfs_block_scores_static_max_bytes": (c_int64, []),
+    "dfs_block_scores_static": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int,
+                                        c_int, c_void_p, c_void_p]),
     "dfs_select_topk": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                 c_void_p, c_int, c_void_p, c_void_p]),
     "dfs_block_sparse_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
@@ -46,7 +49,7 @@ class DfsLibraryError(RuntimeError):
 def _load():
     if not os.path.exists(LIB_PATH):
         raise DfsLibraryError(
-            f"{LIB_PATH} is missing: build it with `python -m dfsattn_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python dfsattn_b200/build.py` "
             "(there is no CPU or PyTorch fallback)")
     lib = ctypes.CDLL(LIB_PATH)
     for table in (SIGNATURES, _DEBUG_SIGNATURES):

@@ -20,6 +20,9 @@ extern "C" const char* dfs_status_string(int code) {
     case DFS_ERR_RANGE: return "argument out of range";
     case DFS_ERR_WORKSPACE: return "workspace too small";
     case DFS_ERR_DRIVER: return "tensor-map encode failed or driver entry point unavailable";
+    case DFS_ERR_STATIC_SCRATCH:
+      return "shape needs more scratch than the 32 MiB built into the library; use dfs_block_scores with a "
+             "caller-provided workspace";
     default: return code > 0 ? "CUDA runtime error" : "unknown error";
   }
 }

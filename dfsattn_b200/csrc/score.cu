@@ -335,3 +335,78 @@ extern "C" int dfs_block_scores(const void* q_perm, const void* k_perm, int dtyp
   block_sum_kernel<<<grid, 256, 0, stream>>>(lse, block_scores, s);
   return static_cast<int>(cudaGetLastError());
 }
+
+// --------------------------------------------------------------------------
+// Scoring without any allocation by the caller or by the library.
+//
+// Some hosts of this library may not allocate device memory at the moment
+// they need block scores: an inference server whose memory pool was sized and
+// frozen at start-up, a plugin that runs inside another framework's step where
+// a cudaMalloc would synchronise the whole device, or a process that has
+// handed all remaining memory to its tensor allocator.  For them the scratch
+// lives in a fixed array inside the loaded library image.  Every GPU that
+// loads the library holds these kStaticScratchBytes until the process exits.
+// --------------------------------------------------------------------------
+namespace {
+constexpr size_t kStaticScratchBytes = 32u << 20;  // 32 MiB
+constexpr int kMaxDevices = 64;
+}  // namespace
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+// Device address of g_static_scratch per device.  In host code the symbol's
+// name is only a handle; the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+char* g_static_scratch_addr[kMaxDevices] = {};
+
+int static_scratch_for_current_device(char** out) {
+  int dev = -1;
+  DFS_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return DFS_ERR_RANGE;
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    DFS_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    if (ptr == nullptr) return DFS_ERR_NULL;
+    g_static_scratch_addr[dev] = static_cast<char*>(ptr);
+  }
+  *out = g_static_scratch_addr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int64_t dfs_block_scores_static_max_bytes(void) { return static_cast<int64_t>(kStaticScratchBytes); }
+
+extern "C" int dfs_block_scores_static(const void* q_perm, const void* k_perm, int dtype, int heads,
+                                       int64_t seq_len, int64_t video_len, int head_dim, int tile, int block,
+                                       int wan_layout, float* block_scores, void* stream_) {
+  if (q_perm == nullptr || k_perm == nullptr || block_scores == nullptr) return DFS_ERR_NULL;
+  if (!dfs_aligned16(q_perm) || !dfs_aligned16(k_perm)) return DFS_ERR_ALIGN;
+  if (dtype != DFS_DTYPE_BF16 && dtype != DFS_DTYPE_F32) return DFS_ERR_DTYPE;
+  const int rc = check_shape(heads, seq_len, video_len, head_dim, tile, block, wan_layout);
+  if (rc != 0) return rc;
+  const ScoreShape s = make_shape(heads, seq_len, video_len, head_dim, wan_layout);
+  const Workspace w = make_workspace(s);
+  if (w.total > kStaticScratchBytes) return DFS_ERR_STATIC_SCRATCH;  // shape needs more than the fixed array
+  char* base = nullptr;
+  const int rs = static_scratch_for_current_device(&base);
+  if (rs != 0) return rs;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  // Nothing in the scratch has to start at zero: the pooling kernel writes every
+  // element of both pooled matrices (padding included) and the block-sum kernel
+  // reads only LSE entries the GEMM kernel has just written, so whatever the
+  // previous call left behind is never read.
+  float* qm = reinterpret_cast<float*>(base + w.qm_off);
+  float* km = reinterpret_cast<float*>(base + w.km_off);
+  float* lse = reinterpret_cast<float*>(base + w.lse_off);
+  int err = dtype == DFS_DTYPE_BF16 ? launch_pool<__nv_bfloat16>(q_perm, k_perm, qm, km, s, stream)
+                                    : launch_pool<float>(q_perm, k_perm, qm, km, s, stream);
+  if (err != 0) return err;
+  const float scale = 1.0f / sqrtf(static_cast<float>(head_dim));
+  err = head_dim == 128 ? launch_lse<128>(qm, km, lse, s, scale, stream)
+                        : launch_lse<64>(qm, km, lse, s, scale, stream);
+  if (err != 0) return err;
+  dim3 grid(s.q_blocks, s.heads);
+  block_sum_kernel<<<grid, 256, 0, stream>>>(lse, block_scores, s);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -139,6 +139,28 @@ def block_scores(q_perm, k_perm, video_len: int, wan_layout: bool, tile=TILE, bl
     return out
 
 
+def block_scores_static(q_perm, k_perm, video_len: int, wan_layout: bool, out: torch.Tensor,
+                        tile=TILE, block=BLOCK) -> torch.Tensor:
+    """Block scores into the caller's ``out`` [H, Rb, Kb] fp32 without allocating
+    anything: scratch is the 32 MiB array built into the library (see
+    ``dfs_block_scores_static`` in include/dfs_b200.h for who needs this and the
+    limits).  Raises ValueError when the shape needs more scratch than that."""
+    _need_cuda(q_perm, k_perm, out)
+    if q_perm.dtype not in _DTYPE_CODE or k_perm.dtype != q_perm.dtype:
+        raise ValueError("scores need bf16 or fp32 inputs")
+    if not (q_perm.is_contiguous() and k_perm.is_contiguous() and out.is_contiguous()):
+        raise ValueError("q, k, out must be contiguous")
+    H, L, D = q_perm.shape
+    kb = math.ceil(L / block)
+    rb = kb if wan_layout else math.ceil(video_len / block)
+    if out.dtype != torch.float32 or tuple(out.shape) != (H, rb, kb):
+        raise ValueError(f"out must be fp32 of shape {(H, rb, kb)}")
+    check(lib.dfs_block_scores_static(q_perm.data_ptr(), k_perm.data_ptr(), _DTYPE_CODE[q_perm.dtype], H, L,
+                                      video_len, D, tile, block, int(wan_layout), out.data_ptr(),
+                                      _stream(q_perm.device)), "dfs_block_scores_static")
+    return out
+
+
 def select_topk(scores, q_rows: int, n_rank: int, k_select: int, dense_row_start: int,
                 want_mask: bool = False):
     """Index lists (idx int32 [H, q_rows, kmax], cnt int32 [H, q_rows]) from fp32

@@ -43,6 +43,8 @@ extern "C" {
 #define DFS_ERR_RANGE -5       /* k / count / length out of range            */
 #define DFS_ERR_WORKSPACE -6   /* workspace too small                        */
 #define DFS_ERR_DRIVER -7      /* tensor-map encode entry point unavailable  */
+#define DFS_ERR_STATIC_SCRATCH -8 /* shape needs more scratch than the fixed
+                                     in-library array of the _static entry point */
 
 /* device status codes written by kernels to *status */
 #define DFS_STATUS_OK 0
@@ -107,6 +109,32 @@ int dfs_block_scores(const void* q_perm, const void* k_perm, int dtype, int head
                      int64_t seq_len, int64_t video_len, int head_dim, int tile, int block,
                      int wan_layout, float* block_scores, void* workspace,
                      int64_t workspace_bytes, void* stream);
+
+/* dfs_block_scores for callers that cannot allocate device memory.
+ * No counterpart in the reference: the reference lets PyTorch allocate its
+ * temporaries freely.  This variant exists for hosts that must not call
+ * cudaMalloc (or any allocating routine) when scores are needed -- a server
+ * whose device memory pool is sized once and then frozen, a plugin invoked
+ * from inside another framework's step where an allocation would stall the
+ * device, a process that has already given all free memory to its tensor
+ * allocator.  Same arguments and results as dfs_block_scores minus the
+ * workspace: the scratch is a fixed array of
+ * dfs_block_scores_static_max_bytes() bytes (32 MiB) inside the library image,
+ * resident on every GPU that loads the library until the process exits.
+ *  - Shapes whose scratch need (dfs_score_workspace_bytes) exceeds that size
+ *    are rejected with DFS_ERR_STATIC_SCRATCH; nothing is launched.
+ *  - The first call on each device looks up the array's device address (with
+ *    that device current); make that first call outside any stream capture.
+ *  - The call allocates nothing and frees nothing.
+ *  - All calls on a device share the one array, which keeps the previous
+ *    call's contents; nothing in it needs to be cleared between calls (every
+ *    element that is read has been written earlier in the same call), but two
+ *    calls whose kernels overlap on the GPU (different streams) race on it:
+ *    serialise them on one stream or with events. */
+int64_t dfs_block_scores_static_max_bytes(void);
+int dfs_block_scores_static(const void* q_perm, const void* k_perm, int dtype, int heads,
+                            int64_t seq_len, int64_t video_len, int head_dim, int tile, int block,
+                            int wan_layout, float* block_scores, void* stream);
 
 /* Per (head, row): the k_select largest of scores[h, r, 0:n_rank) (ties: lowest
  * column first), plus every column in [n_rank, n_cols) ("forced" columns),
