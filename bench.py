@@ -33,6 +33,9 @@ WORKLOADS = {
     "hunyuan_720p": dict(grid=(33, 45, 80), text=256, heads=24, dim=128, sparsity=0.3, flavor="hyvideo"),
     "wan_480p": dict(grid=(21, 30, 52), text=0, heads=40, dim=128, sparsity=0.3, flavor="wan"),
     "wan_720p": dict(grid=(21, 45, 80), text=0, heads=40, dim=128, sparsity=0.3, flavor="wan"),
+    # small cases for ncu captures: inputs still larger than L2 (3 x 67 MB), kernels of a millisecond or two
+    "wan_480p_h8": dict(grid=(21, 30, 52), text=0, heads=8, dim=128, sparsity=0.3, flavor="wan"),
+    "hunyuan_480p_h4": dict(grid=(33, 30, 45), text=256, heads=4, dim=128, sparsity=0.3, flavor="hyvideo"),
     "tiny": dict(grid=(4, 16, 16), text=0, heads=2, dim=64, sparsity=0.3, flavor="hyvideo"),
 }
 METRIC = "dfs_attn_effective_tflops"
