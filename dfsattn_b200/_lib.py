@@ -38,7 +38,6 @@ SIGNATURES = {
 # testing hooks exported by the library but not part of the public header
 _DEBUG_SIGNATURES = {
     "dfs_debug_set_dump": (None, [c_void_p]),
-    "dfs_debug_set_v_desc": (None, [c_uint32, c_uint32]),
 }
 
 

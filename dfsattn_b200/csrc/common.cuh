@@ -64,7 +64,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  Returns false when the wait expired or another thread of the
 // CTA already gave up (*abort_flag != 0); the caller then leaves its loop and
 // goes to the common tear-down.  The limit is in SM clock cycles.
-constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
+constexpr long long kWaitLimitCycles = 400000000LL;  // about 0.2 s
 
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
                                                   volatile int* abort_flag) {

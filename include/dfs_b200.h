@@ -49,6 +49,7 @@ extern "C" {
 /* device status codes written by kernels to *status */
 #define DFS_STATUS_OK 0
 #define DFS_STATUS_WAIT_TIMEOUT 1 /* a bounded barrier wait expired           */
+#define DFS_STATUS_BAD_SMEM_ALIGNMENT 2 /* dynamic shared memory not 1 KB aligned */
 
 int dfs_version(void);
 const char* dfs_status_string(int code);
