@@ -25,10 +25,10 @@ SIGNATURES = {
     "dfs_unpermute": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_void_p]),
     "dfs_score_workspace_bytes": (c_int64, [c_int, c_int64, c_int64, c_int, c_int, c_int, c_int]),
     "dfs_block_scores": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int,
-                                 c_int, c_void_p, c_void_p, c_int64, c_void_p]),
+                                 c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "dfs_block_scores_static_max_bytes": (c_int64, []),
     "dfs_block_scores_static": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int,
-                                        c_int, c_void_p, c_void_p]),
+                                        c_int, c_void_p, c_void_p, c_void_p]),
     "dfs_select_topk": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                 c_void_p, c_int, c_void_p, c_void_p]),
     "dfs_block_sparse_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,

@@ -3,27 +3,34 @@
 //
 // The softmax-ed tile-score tensor of the reference ([H, 7432, 7448] at the
 // 720p shape, several GB) is never materialised.  Three kernels:
-//   1. pool_tiles_kernel : means of 16 consecutive (scoring-layout) tokens,
-//                          written d-major so that the GEMM reads them coalesced.
-//   2. tile_lse_kernel   : fp32 GEMM of pooled Q x pooled K; for every (query
-//                          tile, key BLOCK) only log-sum-exp of the 8 logits
-//                          of that block is kept  (H * Nq * Kb floats).
+//   1. pool_tiles_kernel : fp32 means of 16 consecutive (scoring-layout)
+//                          tokens, stored as TWO bf16 matrices per tensor: the
+//                          rounded mean ("hi") and the rounded remainder
+//                          ("lo"), 16 significant bits together.
+//   2. tile_lse_kernel   : pooled logits on tcgen05 tensor cores, fp32
+//                          accumulate in TMEM: Qhi.Khi + Qhi.Klo + Qlo.Khi (the
+//                          dropped lo.lo term is below 2^-16 relative).  For
+//                          every (query tile, key BLOCK) only the base-2
+//                          log-sum-exp of the 8 scaled logits of that block is
+//                          kept  (H * Nq * Kb floats).
 //   3. block_sum_kernel  : per query block, row max / normaliser over all key
 //                          blocks from the stored LSEs, then
-//                          B[c] = sum_i exp(lse_ic - M_i) / Z_i   (= the sum of
+//                          B[c] = sum_i 2^(lse_ic - M_i) / Z_i   (= the sum of
 //                          the 64 softmax-ed tile scores of the 8x8 group).
-// Everything is fp32; sums of softmax-ed scores equal the reference's up to
-// fp32 rounding (different summation order).
+// Sums of softmax-ed scores equal the reference's fp32 results up to rounding
+// (different summation order, 2^-16 operand split).
 #include <math.h>
 
 #include "common.cuh"
 
 namespace {
 
+using namespace dfs;
+
 constexpr int kTile = 16;    // tokens per pooled tile
 constexpr int kBlock = 128;  // tokens per block
 constexpr int kTilesPerBlock = kBlock / kTile;
-constexpr int kGemmTile = 64;  // pooled rows per GEMM tile (= 8 blocks)
+constexpr int kGemmTile = 128;  // pooled rows / columns per MMA tile (= 16 blocks)
 
 struct ScoreShape {
   int heads;
@@ -54,14 +61,16 @@ __host__ ScoreShape make_shape(int heads, int64_t seq_len, int64_t video_len, in
 
 __host__ size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 
+// scratch layout: pooled Q as bf16 [2H][nq_pad][D] (plane 2h = hi, 2h+1 = lo), pooled K likewise,
+// then the per-(query tile, key block) log-sum-exp values fp32 [H][nq][Kb]
 struct Workspace {
   size_t qm_off, km_off, lse_off, total;
 };
 __host__ Workspace make_workspace(const ScoreShape& s) {
   Workspace w;
   w.qm_off = 0;
-  w.km_off = align256(w.qm_off + sizeof(float) * s.heads * s.head_dim * static_cast<size_t>(s.nq_pad));
-  w.lse_off = align256(w.km_off + sizeof(float) * s.heads * s.head_dim * static_cast<size_t>(s.nk_pad));
+  w.km_off = align256(w.qm_off + 2 * sizeof(__nv_bfloat16) * s.heads * s.head_dim * static_cast<size_t>(s.nq_pad));
+  w.lse_off = align256(w.km_off + 2 * sizeof(__nv_bfloat16) * s.heads * s.head_dim * static_cast<size_t>(s.nk_pad));
   w.total = align256(w.lse_off + sizeof(float) * s.heads * static_cast<size_t>(s.nq) * s.k_blocks);
   return w;
 }
@@ -101,33 +110,31 @@ struct Vec16<float> {
   }
 };
 
-// One thread: one 16-byte column chunk of one pooled tile.  A CTA covers
-// TILES_PER_CTA consecutive tiles; results go through shared memory so that the
-// d-major output is written as runs of TILES_PER_CTA consecutive floats.
+// One thread: one 16-byte column chunk of one pooled tile (16 rows summed in fp32), written as
+// bf16 hi / lo rows.  Padding tiles are written as zeros.
 template <typename T>
 __global__ void __launch_bounds__(256) pool_tiles_kernel(const T* __restrict__ q, const T* __restrict__ k,
-                                                         float* __restrict__ qm_t, float* __restrict__ km_t,
-                                                         ScoreShape s) {
+                                                         __nv_bfloat16* __restrict__ qm,
+                                                         __nv_bfloat16* __restrict__ km, ScoreShape s) {
   constexpr int E = Vec16<T>::kElems;
-  const int chunks = s.head_dim / E;          // 16-byte chunks per row
+  const int chunks = s.head_dim / E;  // 16-byte chunks per input row
   const int tiles_per_cta = blockDim.x / chunks;
-  extern __shared__ float sm_pool[];          // [head_dim][tiles_per_cta + 1]
-  const int which = blockIdx.z;               // 0: Q, 1: K
+  const int which = blockIdx.z;       // 0: Q, 1: K
   const int head = blockIdx.y;
   const int n_tiles = which == 0 ? s.nq : s.nk;
   const int n_pad = which == 0 ? s.nq_pad : s.nk_pad;
   const T* __restrict__ src = (which == 0 ? q : k) + static_cast<size_t>(head) * s.seq_len * s.head_dim;
-  float* __restrict__ dst = (which == 0 ? qm_t : km_t) + static_cast<size_t>(head) * s.head_dim * n_pad;
+  __nv_bfloat16* __restrict__ dst_hi =
+      (which == 0 ? qm : km) + static_cast<size_t>(2 * head) * n_pad * s.head_dim;
+  __nv_bfloat16* __restrict__ dst_lo = dst_hi + static_cast<size_t>(n_pad) * s.head_dim;
 
-  const int tile0 = blockIdx.x * tiles_per_cta;
-  if (tile0 >= n_pad) return;
-  const int tl = threadIdx.x / chunks;
+  const int tile = blockIdx.x * tiles_per_cta + threadIdx.x / chunks;
   const int ch = threadIdx.x % chunks;
-  const int tile = tile0 + tl;
+  if (tile >= n_pad) return;
   float acc[E];
 #pragma unroll
   for (int i = 0; i < E; ++i) acc[i] = 0.f;
-  if (tl < tiles_per_cta && tile < n_tiles) {
+  if (tile < n_tiles) {
     const long long p0 = static_cast<long long>(tile) * kTile;
 #pragma unroll 4
     for (int r = 0; r < kTile; ++r) {
@@ -138,94 +145,220 @@ __global__ void __launch_bounds__(256) pool_tiles_kernel(const T* __restrict__ q
       }
     }
   }
-  const int ld = tiles_per_cta + 1;
-  if (tl < tiles_per_cta) {
+  __nv_bfloat16 hi[E], lo[E];
 #pragma unroll
-    for (int i = 0; i < E; ++i) sm_pool[(ch * E + i) * ld + tl] = acc[i] * (1.0f / kTile);
+  for (int i = 0; i < E; ++i) {
+    const float mean = acc[i] * (1.0f / kTile);
+    hi[i] = __float2bfloat16_rn(mean);
+    lo[i] = __float2bfloat16_rn(mean - __bfloat162float(hi[i]));
   }
-  __syncthreads();
-  for (int e = threadIdx.x; e < s.head_dim * tiles_per_cta; e += blockDim.x) {
-    const int d = e / tiles_per_cta;
-    const int t = e - d * tiles_per_cta;
-    if (tile0 + t < n_pad) dst[static_cast<size_t>(d) * n_pad + tile0 + t] = sm_pool[d * ld + t];
+  const size_t at = static_cast<size_t>(tile) * s.head_dim + ch * E;
+  if constexpr (E == 8) {
+    *reinterpret_cast<uint4*>(dst_hi + at) = *reinterpret_cast<const uint4*>(hi);
+    *reinterpret_cast<uint4*>(dst_lo + at) = *reinterpret_cast<const uint4*>(lo);
+  } else {
+    *reinterpret_cast<uint2*>(dst_hi + at) = *reinterpret_cast<const uint2*>(hi);
+    *reinterpret_cast<uint2*>(dst_lo + at) = *reinterpret_cast<const uint2*>(lo);
   }
 }
 
-// 64 x 64 pooled logits per step, 4 x 4 per thread, fp32 FMA.
+// --------------------------------------------------------------------------
+// pooled logits on tcgen05 + per-block log-sum-exp epilogue
+//
+// One CTA per (128 pooled query rows, head); it walks all 128-column tiles of pooled keys.
+//   warp 0   TMA producer: Q hi/lo once, K hi/lo tiles through a 2-stage ring
+//   warp 1   MMA issuer (one lane): 3 x D/16 MMAs per column tile into one of two TMEM buffers
+//   warps 2-5 epilogue: one thread per pooled query row reads the 128 logits (tcgen05.ld) and
+//            reduces each group of 8 (one key block) to a base-2 log-sum-exp
+// Every wait is bounded; an expired wait sets *status and the CTA leaves through the common tear-down.
+// --------------------------------------------------------------------------
+constexpr int kLseThreads = 192;
+constexpr int kLseStages = 2;
+
 template <int HD>
-__global__ void __launch_bounds__(256) tile_lse_kernel(const float* __restrict__ qm_t,
-                                                       const float* __restrict__ km_t,
-                                                       float* __restrict__ lse, ScoreShape s, float scale) {
-  extern __shared__ float sm_gemm[];
-  float* As = sm_gemm;                   // [HD][64]
-  float* Bs = sm_gemm + HD * kGemmTile;  // [HD][64]
+struct LseSmem {
+  static constexpr int kBoxBytes = 128 * 64 * 2;
+  static constexpr int kTileBytes = kBoxBytes * (HD / 64);   // one 128-row bf16 tile (hi or lo)
+  static constexpr int kQOff = 0;                            // hi, lo
+  static constexpr int kKOff = 2 * kTileBytes;               // [stage][hi, lo]
+  static constexpr int kBarOff = kKOff + kLseStages * 2 * kTileBytes;
+  static constexpr int kNumBars = 1 + 2 * kLseStages + 2 + 2 + 1;
+  static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+  static constexpr int kTotal = kMiscOff + 16;
+};
+
+__device__ __forceinline__ float lg2_approx(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kLseThreads, 1)
+    tile_lse_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                    float* __restrict__ lse, ScoreShape s, float scale_log2, int32_t* status) {
+  using L = LseSmem<HD>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0 && status) atomicExch(status, DFS_STATUS_BAD_SMEM_ALIGNMENT);
+    return;
+  }
+  if (status != nullptr && *reinterpret_cast<volatile int32_t*>(status) != 0) return;
+  uint8_t* q_tiles = smem + L::kQOff;
+  uint8_t* k_ring = smem + L::kKOff;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;               // [2]
+  uint64_t* k_empty = k_full + kLseStages;   // [2]
+  uint64_t* s_full = k_empty + kLseStages;   // [2]  logits of a column tile are in TMEM buffer b
+  uint64_t* s_empty = s_full + 2;            // [2]  the epilogue has read buffer b
+  uint64_t* mma_drain = s_empty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y;
   const int row0 = blockIdx.x * kGemmTile;
-  const int tx = threadIdx.x & 15;
-  const int ty = threadIdx.x >> 4;
-  const float* __restrict__ a_src = qm_t + static_cast<size_t>(head) * HD * s.nq_pad + row0;
-  const float* __restrict__ b_src = km_t + static_cast<size_t>(head) * HD * s.nk_pad;
+  const int n_ct = s.nk_pad / kGemmTile;  // column tiles
 
-  for (int e = threadIdx.x; e < HD * (kGemmTile / 4); e += 256) {
-    const int d = e / (kGemmTile / 4);
-    const int c4 = e - d * (kGemmTile / 4);
-    reinterpret_cast<float4*>(As)[e] =
-        __ldg(reinterpret_cast<const float4*>(a_src + static_cast<size_t>(d) * s.nq_pad) + c4);
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < kLseStages; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1);
+      mbar_init(&s_empty[b], 4);  // one arrival per epilogue warp
+    }
+    mbar_init(mma_drain, 1);
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      mbar_arrive_expect_tx(q_full, 2 * L::kTileBytes);
+      for (int part = 0; part < 2; ++part)
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_3d(q_tiles + part * L::kTileBytes + c * L::kBoxBytes, &tm_q, q_full, c * 64, row0,
+                      2 * head + part);
+      bool ok = true;
+      int issued = 0;
+      for (int ct = 0; ct < n_ct; ++ct) {
+        const int st = ct % kLseStages;
+        ok = mbar_wait_bounded(&k_empty[st], ((ct / kLseStages) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&k_full[st], 2 * L::kTileBytes);
+        for (int part = 0; part < 2; ++part)
+          for (int c = 0; c < HD / 64; ++c)
+            tma_load_3d(k_ring + (st * 2 + part) * L::kTileBytes + c * L::kBoxBytes, &tm_k, &k_full[st], c * 64,
+                        ct * kGemmTile, 2 * head + part);
+        ++issued;
+      }
+      if (!ok) {
+        mbar_wait_bounded(q_full, 0, abort_flag + 1);
+        for (int ct = issued > kLseStages ? issued - kLseStages : 0; ct < issued; ++ct)
+          mbar_wait_bounded(&k_full[ct % kLseStages], (ct / kLseStages) & 1, abort_flag + 1);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(128, 128, 0, 0);
+      const uint64_t q_hi = umma_desc_sw128(smem_u32(q_tiles), 16, 1024);
+      const uint64_t q_lo = q_hi + (L::kTileBytes >> 4);
+      const uint64_t k_desc0 = umma_desc_sw128(smem_u32(k_ring), 16, 1024);
+      bool ok = mbar_wait_bounded(q_full, 0, abort_flag);
+      for (int ct = 0; ct < n_ct && ok; ++ct) {
+        const int st = ct % kLseStages, b = ct & 1;
+        ok = mbar_wait_bounded(&k_full[st], (ct / kLseStages) & 1, abort_flag);
+        if (!ok) break;
+        ok = mbar_wait_bounded(&s_empty[b], ((ct >> 1) & 1) ^ 1, abort_flag);  // passes at once the first time
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint64_t k_hi = k_desc0 + static_cast<uint64_t>(st * 2) * (L::kTileBytes >> 4);
+        const uint64_t k_lo = k_hi + (L::kTileBytes >> 4);
+        const uint32_t d_tmem = tmem_base + b * 128;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint64_t off = (ks / 4) * (L::kBoxBytes >> 4) + (ks % 4) * 2;
+          umma_ss(d_tmem, q_hi + off, k_hi + off, idesc, ks > 0);
+          umma_ss(d_tmem, q_hi + off, k_lo + off, idesc, 1);
+          umma_ss(d_tmem, q_lo + off, k_hi + off, idesc, 1);
+        }
+        umma_commit(&k_empty[st]);
+        umma_commit(&s_full[b]);
+      }
+      if (!ok) {
+        umma_commit(mma_drain);
+        mbar_wait_bounded(mma_drain, 0, abort_flag + 1);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = row0 + quad * 32 + lane;
+    const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
+    float* __restrict__ out_row = lse + (static_cast<size_t>(head) * s.nq + (row < s.nq ? row : 0)) * s.k_blocks;
+    bool ok = true;
+    for (int ct = 0; ct < n_ct; ++ct) {
+      const int b = ct & 1;
+      ok = mbar_wait_bounded(&s_full[b], (ct >> 1) & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + lane_sel + b * 128 + g * 32, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int grp = 0; grp < 4; ++grp) {
+          float v[8];
+          float m = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            v[i] = __uint_as_float(r[grp * 8 + i]) * scale_log2;
+            m = fmaxf(m, v[i]);
+          }
+          float sum = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sum += ex2_approx(v[i] - m);
+          const int kb = ct * (kGemmTile / kTilesPerBlock) + g * 4 + grp;
+          if (row < s.nq && kb < s.k_blocks) out_row[kb] = m + lg2_approx(sum);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[b]);
+    }
   }
 
-  for (int col0 = 0; col0 < s.nk_pad; col0 += kGemmTile) {
-    __syncthreads();  // previous step's readers of Bs are done (also covers As on the first step)
-    for (int e = threadIdx.x; e < HD * (kGemmTile / 4); e += 256) {
-      const int d = e / (kGemmTile / 4);
-      const int c4 = e - d * (kGemmTile / 4);
-      reinterpret_cast<float4*>(Bs)[e] =
-          __ldg(reinterpret_cast<const float4*>(b_src + static_cast<size_t>(d) * s.nk_pad + col0) + c4);
-    }
-    __syncthreads();
-
-    float acc[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-
-#pragma unroll 8
-    for (int d = 0; d < HD; ++d) {
-      const float4 a = reinterpret_cast<const float4*>(As + d * kGemmTile)[ty];
-      const float4 b = reinterpret_cast<const float4*>(Bs + d * kGemmTile)[tx];
-      const float av[4] = {a.x, a.y, a.z, a.w};
-      const float bv[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
-    }
-
-    // log-sum-exp over the 8 key tiles of one key block: 4 here, 4 in lane^1
-    const int kblock = (col0 + tx * 4) / kTilesPerBlock;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float m = -INFINITY;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        acc[i][j] *= scale;
-        m = fmaxf(m, acc[i][j]);
-      }
-      float sum = 0.f;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) sum += expf(acc[i][j] - m);
-      const float m2 = __shfl_xor_sync(0xffffffffu, m, 1);
-      const float s2 = __shfl_xor_sync(0xffffffffu, sum, 1);
-      const float mm = fmaxf(m, m2);
-      const float tot = sum * expf(m - mm) + s2 * expf(m2 - mm);
-      const int row = row0 + ty * 4 + i;
-      if ((tx & 1) == 0 && row < s.nq && kblock < s.k_blocks)
-        lse[(static_cast<size_t>(head) * s.nq + row) * s.k_blocks + kblock] = mm + logf(tot);
-    }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (abort_flag[0] != 0 && threadIdx.x == 0 && status) atomicExch(status, DFS_STATUS_WAIT_TIMEOUT);
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 256);
   }
 }
 
-// One CTA per (query block, head): 8 pooled rows x Kb stored LSEs -> Kb block scores.
+// One CTA per (query block, head): 8 pooled rows x Kb stored base-2 LSEs -> Kb block scores.
 __global__ void __launch_bounds__(256) block_sum_kernel(const float* __restrict__ lse,
                                                         float* __restrict__ block_scores, ScoreShape s) {
   __shared__ float row_max[kTilesPerBlock];
@@ -241,7 +374,7 @@ __global__ void __launch_bounds__(256) block_sum_kernel(const float* __restrict_
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     float z = 0.f;
-    for (int c = lane; c < s.k_blocks; c += 32) z += expf(r[c] - m);
+    for (int c = lane; c < s.k_blocks; c += 32) z += exp2f(r[c] - m);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
     if (lane == 0) {
@@ -255,30 +388,33 @@ __global__ void __launch_bounds__(256) block_sum_kernel(const float* __restrict_
     float b = 0.f;
 #pragma unroll
     for (int i = 0; i < kTilesPerBlock; ++i)
-      b += expf(rows[static_cast<size_t>(i) * s.k_blocks + c] - row_max[i]) * row_inv[i];
+      b += exp2f(rows[static_cast<size_t>(i) * s.k_blocks + c] - row_max[i]) * row_inv[i];
     out[c] = b;
   }
 }
 
 template <typename T>
-int launch_pool(const void* q, const void* k, float* qm, float* km, const ScoreShape& s, cudaStream_t stream) {
+int launch_pool(const void* q, const void* k, __nv_bfloat16* qm, __nv_bfloat16* km, const ScoreShape& s,
+                cudaStream_t stream) {
   const int chunks = s.head_dim / Vec16<T>::kElems;
   const int tiles_per_cta = 256 / chunks;
   const int n_pad = s.nk_pad > s.nq_pad ? s.nk_pad : s.nq_pad;
   dim3 grid((n_pad + tiles_per_cta - 1) / tiles_per_cta, s.heads, 2);
-  const size_t smem = sizeof(float) * s.head_dim * (tiles_per_cta + 1);
-  pool_tiles_kernel<T><<<grid, 256, smem, stream>>>(static_cast<const T*>(q), static_cast<const T*>(k), qm, km, s);
+  pool_tiles_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(q), static_cast<const T*>(k), qm, km, s);
   return static_cast<int>(cudaGetLastError());
 }
 
 template <int HD>
-int launch_lse(const float* qm, const float* km, float* lse, const ScoreShape& s, float scale,
-               cudaStream_t stream) {
-  const size_t smem = sizeof(float) * 2 * HD * kGemmTile;
-  DFS_CUDA_CHECK(cudaFuncSetAttribute(tile_lse_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      static_cast<int>(smem)));
+int launch_lse(const __nv_bfloat16* qm, const __nv_bfloat16* km, float* lse, const ScoreShape& s, float scale_log2,
+               int32_t* status, cudaStream_t stream) {
+  using L = LseSmem<HD>;
+  CUtensorMap mq, mk;
+  int rc = dfs_make_bf16_tile_map(&mq, qm, 2 * s.heads, s.nq_pad, HD);
+  if (rc == 0) rc = dfs_make_bf16_tile_map(&mk, km, 2 * s.heads, s.nk_pad, HD);
+  if (rc != 0) return rc;
+  DFS_CUDA_CHECK(cudaFuncSetAttribute(tile_lse_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
   dim3 grid(s.nq_pad / kGemmTile, s.heads);
-  tile_lse_kernel<HD><<<grid, 256, smem, stream>>>(qm, km, lse, s, scale);
+  tile_lse_kernel<HD><<<grid, kLseThreads, L::kTotal, stream>>>(mq, mk, lse, s, scale_log2, status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -286,7 +422,7 @@ int check_shape(int heads, int64_t seq_len, int64_t video_len, int head_dim, int
                 int wan_layout) {
   if (tile != kTile || block != kBlock) return DFS_ERR_SHAPE;
   if (head_dim != 64 && head_dim != 128) return DFS_ERR_SHAPE;
-  if (heads <= 0 || seq_len <= 0) return DFS_ERR_SHAPE;
+  if (heads <= 0 || heads > 32767 || seq_len <= 0) return DFS_ERR_SHAPE;
   if (!wan_layout) {
     if (video_len <= 0 || video_len > seq_len) return DFS_ERR_RANGE;
     // The scoring layout [video | zero gap | text] must fit in Kb blocks; the
@@ -295,6 +431,25 @@ int check_shape(int heads, int64_t seq_len, int64_t video_len, int head_dim, int
     if (vb * kBlock + (seq_len - video_len) > kb * kBlock) return DFS_ERR_SHAPE;
   }
   return 0;
+}
+
+// pool -> tensor-core logits + per-block LSE -> block sums, on scratch of make_workspace(s).total bytes
+int run_block_scores(const void* q_perm, const void* k_perm, int dtype, const ScoreShape& s, float* block_scores,
+                     char* base, int32_t* status, cudaStream_t stream) {
+  const Workspace w = make_workspace(s);
+  __nv_bfloat16* qm = reinterpret_cast<__nv_bfloat16*>(base + w.qm_off);
+  __nv_bfloat16* km = reinterpret_cast<__nv_bfloat16*>(base + w.km_off);
+  float* lse = reinterpret_cast<float*>(base + w.lse_off);
+  int err = dtype == DFS_DTYPE_BF16 ? launch_pool<__nv_bfloat16>(q_perm, k_perm, qm, km, s, stream)
+                                    : launch_pool<float>(q_perm, k_perm, qm, km, s, stream);
+  if (err != 0) return err;
+  const float scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(s.head_dim));
+  err = s.head_dim == 128 ? launch_lse<128>(qm, km, lse, s, scale_log2, status, stream)
+                          : launch_lse<64>(qm, km, lse, s, scale_log2, status, stream);
+  if (err != 0) return err;
+  dim3 grid(s.q_blocks, s.heads);
+  block_sum_kernel<<<grid, 256, 0, stream>>>(lse, block_scores, s);
+  return static_cast<int>(cudaGetLastError());
 }
 
 }  // namespace
@@ -308,32 +463,20 @@ extern "C" int64_t dfs_score_workspace_bytes(int heads, int64_t seq_len, int64_t
 
 extern "C" int dfs_block_scores(const void* q_perm, const void* k_perm, int dtype, int heads, int64_t seq_len,
                                 int64_t video_len, int head_dim, int tile, int block, int wan_layout,
-                                float* block_scores, void* workspace, int64_t workspace_bytes, void* stream_) {
+                                float* block_scores, void* workspace, int64_t workspace_bytes, int32_t* status,
+                                void* stream_) {
   if (q_perm == nullptr || k_perm == nullptr || block_scores == nullptr || workspace == nullptr)
     return DFS_ERR_NULL;
-  if (!dfs_aligned16(q_perm) || !dfs_aligned16(k_perm) || !dfs_aligned16(workspace)) return DFS_ERR_ALIGN;
+  if (!dfs_aligned16(q_perm) || !dfs_aligned16(k_perm) || (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+    return DFS_ERR_ALIGN;
   if (dtype != DFS_DTYPE_BF16 && dtype != DFS_DTYPE_F32) return DFS_ERR_DTYPE;
   const int rc = check_shape(heads, seq_len, video_len, head_dim, tile, block, wan_layout);
   if (rc != 0) return rc;
   const ScoreShape s = make_shape(heads, seq_len, video_len, head_dim, wan_layout);
   const Workspace w = make_workspace(s);
   if (workspace_bytes < static_cast<int64_t>(w.total)) return DFS_ERR_WORKSPACE;
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  char* base = static_cast<char*>(workspace);
-  float* qm = reinterpret_cast<float*>(base + w.qm_off);
-  float* km = reinterpret_cast<float*>(base + w.km_off);
-  float* lse = reinterpret_cast<float*>(base + w.lse_off);
-
-  int err = dtype == DFS_DTYPE_BF16 ? launch_pool<__nv_bfloat16>(q_perm, k_perm, qm, km, s, stream)
-                                    : launch_pool<float>(q_perm, k_perm, qm, km, s, stream);
-  if (err != 0) return err;
-  const float scale = 1.0f / sqrtf(static_cast<float>(head_dim));
-  err = head_dim == 128 ? launch_lse<128>(qm, km, lse, s, scale, stream)
-                        : launch_lse<64>(qm, km, lse, s, scale, stream);
-  if (err != 0) return err;
-  dim3 grid(s.q_blocks, s.heads);
-  block_sum_kernel<<<grid, 256, 0, stream>>>(lse, block_scores, s);
-  return static_cast<int>(cudaGetLastError());
+  return run_block_scores(q_perm, k_perm, dtype, s, block_scores, static_cast<char*>(workspace), status,
+                          static_cast<cudaStream_t>(stream_));
 }
 
 // --------------------------------------------------------------------------
@@ -379,7 +522,7 @@ extern "C" int64_t dfs_block_scores_static_max_bytes(void) { return static_cast<
 
 extern "C" int dfs_block_scores_static(const void* q_perm, const void* k_perm, int dtype, int heads,
                                        int64_t seq_len, int64_t video_len, int head_dim, int tile, int block,
-                                       int wan_layout, float* block_scores, void* stream_) {
+                                       int wan_layout, float* block_scores, int32_t* status, void* stream_) {
   if (q_perm == nullptr || k_perm == nullptr || block_scores == nullptr) return DFS_ERR_NULL;
   if (!dfs_aligned16(q_perm) || !dfs_aligned16(k_perm)) return DFS_ERR_ALIGN;
   if (dtype != DFS_DTYPE_BF16 && dtype != DFS_DTYPE_F32) return DFS_ERR_DTYPE;
@@ -391,22 +534,10 @@ extern "C" int dfs_block_scores_static(const void* q_perm, const void* k_perm, i
   char* base = nullptr;
   const int rs = static_scratch_for_current_device(&base);
   if (rs != 0) return rs;
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   // Nothing in the scratch has to start at zero: the pooling kernel writes every
-  // element of both pooled matrices (padding included) and the block-sum kernel
-  // reads only LSE entries the GEMM kernel has just written, so whatever the
+  // element of the pooled matrices (padding included) and the block-sum kernel
+  // reads only LSE entries the logits kernel has just written, so whatever the
   // previous call left behind is never read.
-  float* qm = reinterpret_cast<float*>(base + w.qm_off);
-  float* km = reinterpret_cast<float*>(base + w.km_off);
-  float* lse = reinterpret_cast<float*>(base + w.lse_off);
-  int err = dtype == DFS_DTYPE_BF16 ? launch_pool<__nv_bfloat16>(q_perm, k_perm, qm, km, s, stream)
-                                    : launch_pool<float>(q_perm, k_perm, qm, km, s, stream);
-  if (err != 0) return err;
-  const float scale = 1.0f / sqrtf(static_cast<float>(head_dim));
-  err = head_dim == 128 ? launch_lse<128>(qm, km, lse, s, scale, stream)
-                        : launch_lse<64>(qm, km, lse, s, scale, stream);
-  if (err != 0) return err;
-  dim3 grid(s.q_blocks, s.heads);
-  block_sum_kernel<<<grid, 256, 0, stream>>>(lse, block_scores, s);
-  return static_cast<int>(cudaGetLastError());
+  return run_block_scores(q_perm, k_perm, dtype, s, block_scores, base, status,
+                          static_cast<cudaStream_t>(stream_));
 }

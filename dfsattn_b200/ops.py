@@ -135,7 +135,8 @@ def block_scores(q_perm, k_perm, video_len: int, wan_layout: bool, tile=TILE, bl
     check(lib.dfs_block_scores(q_perm.data_ptr(), k_perm.data_ptr(), _DTYPE_CODE[q_perm.dtype], H, L,
                                video_len, D, tile, block, int(wan_layout), out.data_ptr(),
                                workspace.data_ptr(), workspace.numel() * workspace.element_size(),
-                               _stream(q_perm.device)), "dfs_block_scores")
+                               status_tensor(q_perm.device).data_ptr(), _stream(q_perm.device)),
+          "dfs_block_scores")
     return out
 
 
@@ -157,7 +158,8 @@ def block_scores_static(q_perm, k_perm, video_len: int, wan_layout: bool, out: t
         raise ValueError(f"out must be fp32 of shape {(H, rb, kb)}")
     check(lib.dfs_block_scores_static(q_perm.data_ptr(), k_perm.data_ptr(), _DTYPE_CODE[q_perm.dtype], H, L,
                                       video_len, D, tile, block, int(wan_layout), out.data_ptr(),
-                                      _stream(q_perm.device)), "dfs_block_scores_static")
+                                      status_tensor(q_perm.device).data_ptr(), _stream(q_perm.device)),
+          "dfs_block_scores_static")
     return out
 
 

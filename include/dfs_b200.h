@@ -104,12 +104,14 @@ int64_t dfs_score_workspace_bytes(int heads, int64_t seq_len, int64_t video_len,
  * between video and text, query tiles cover the video part only) and
  * dfsattn/attention_wan.py:157-209,243-246 (wan_layout != 0: zero pad at the
  * end only, query tiles cover everything).  q, k are the PERMUTED tensors
- * [H, L, D] (bf16 or f32); means, logits and softmax are computed in fp32.
- * tile must be 16 and block 128. */
+ * [H, L, D] (bf16 or f32).  Means are fp32, carried into the tensor-core
+ * product as a bf16 hi + lo pair (16 significant bits), logits accumulate in
+ * fp32, softmax and sums are fp32.  tile must be 16 and block 128; workspace
+ * 256-byte aligned; status: device int32, zero-initialised by the caller. */
 int dfs_block_scores(const void* q_perm, const void* k_perm, int dtype, int heads,
                      int64_t seq_len, int64_t video_len, int head_dim, int tile, int block,
                      int wan_layout, float* block_scores, void* workspace,
-                     int64_t workspace_bytes, void* stream);
+                     int64_t workspace_bytes, int32_t* status, void* stream);
 
 /* dfs_block_scores for callers that cannot allocate device memory.
  * No counterpart in the reference: the reference lets PyTorch allocate its
@@ -135,7 +137,7 @@ int dfs_block_scores(const void* q_perm, const void* k_perm, int dtype, int head
 int64_t dfs_block_scores_static_max_bytes(void);
 int dfs_block_scores_static(const void* q_perm, const void* k_perm, int dtype, int heads,
                             int64_t seq_len, int64_t video_len, int head_dim, int tile, int block,
-                            int wan_layout, float* block_scores, void* stream);
+                            int wan_layout, float* block_scores, int32_t* status, void* stream);
 
 /* Per (head, row): the k_select largest of scores[h, r, 0:n_rank) (ties: lowest
  * column first), plus every column in [n_rank, n_cols) ("forced" columns),
