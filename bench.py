@@ -217,8 +217,21 @@ def run_gpu(args, spec, rank, local_rank, world):
         raise SystemExit(f"{H} heads do not split over {world} ranks")
     h_local = H // world
     f, h, w = spec["grid"]
-    q, k, v = structured_qkv(spec["grid"], h_local, D, text_len=spec["text"], dtype=torch.bfloat16, device=dev,
-                             seed=0, head_offset=rank * h_local, total_heads=H)
+    seq_layout = args.layout == "seq" and world > 1
+    if seq_layout:
+        # sequence-sharded inputs: every rank holds all heads for its contiguous range of raster tokens
+        from dfsattn_b200 import parallel
+        qf, kf, vf = structured_qkv(spec["grid"], H, D, text_len=spec["text"], dtype=torch.bfloat16, device=dev,
+                                    seed=0)
+        L = qf.shape[2]
+        t0, tn = parallel.seq_shard(L, rank, world)
+        q_seq, k_seq, v_seq = (t[:, :, t0:t0 + tn].contiguous() for t in (qf, kf, vf))
+        h0 = rank * h_local
+        q, k, v = (t[:, h0:h0 + h_local].contiguous() for t in (qf, kf, vf))   # for the per-stage timings
+        del qf, kf, vf
+    else:
+        q, k, v = structured_qkv(spec["grid"], h_local, D, text_len=spec["text"], dtype=torch.bfloat16,
+                                 device=dev, seed=0, head_offset=rank * h_local, total_heads=H)
     L = q.shape[2]
     video_len = L - spec["text"]
     vperm = hilbert3d_perm(f, h, w)
@@ -235,9 +248,18 @@ def run_gpu(args, spec, rank, local_rank, world):
                              sparsity=spec["sparsity"], sparsity_dcrt=0.1, tile_size=16, block_size=128,
                              video_perm=vperm)
 
+    if seq_layout:
+        head_call = call
+
+        def call(qq, kk, vv):  # noqa: F811  one all-to-all in (Q,K,V together), one out
+            return parallel.dfs_attention_sequence_parallel(qq, kk, vv, L, head_call)
+        step_inputs = (q_seq, k_seq, v_seq)
+    else:
+        step_inputs = (q, k, v)
+
     Attn.clear_cache()
     for _ in range(max(args.warmup, 3)):
-        out = call(q, k, v)
+        out = call(*step_inputs)
     torch.cuda.synchronize()
     ops.check_status(dev)
     lists = next(iter(Attn._cached_metadata.values()))["block_lists"]
@@ -247,7 +269,7 @@ def run_gpu(args, spec, rank, local_rank, world):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    secs = timed(lambda: call(q, k, v), args.steps, barrier)
+    secs = timed(lambda: call(*step_inputs), args.steps, barrier)
     secs = reduce(secs, dist.ReduceOp.MAX if world > 1 else None)
     clocks = sampler.stop() if rank == 0 else None
     ops.check_status(dev)
@@ -277,9 +299,9 @@ def run_gpu(args, spec, rank, local_rank, world):
     }
 
     # ---- end to end through the public API with HOST buffers ----------------
-    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    hq, hk, hv = (t.cpu().pin_memory() for t in step_inputs)
     hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    dq, dk, dv = (torch.empty_like(t) for t in (q, k, v))
+    dq, dk, dv = (torch.empty_like(t) for t in step_inputs)
 
     def e2e_step():
         dq.copy_(hq, non_blocking=True)
@@ -294,6 +316,8 @@ def run_gpu(args, spec, rank, local_rank, world):
     ops.check_status(dev)
     e2e = {"value": flops_total / e_secs / 1e12, "unit": UNIT, "ms_per_call": 1e3 * e_secs,
            "h2d_bytes_per_step": 3 * tensor_bytes * world, "d2h_bytes_per_step": tensor_bytes * world}
+    if world > 1:
+        dist.barrier()
 
     if rank == 0:
         cpu = None
@@ -310,7 +334,9 @@ def run_gpu(args, spec, rank, local_rank, world):
                        "seq_len": L, "heads": H, "heads_per_gpu": h_local, "head_dim": D,
                        "sparsity": spec["sparsity"], "order": "hilbert3d", "block": 128, "tile": 16,
                        "step": "refresh call: permute + score + select + attention (+fused unpermute)",
-                       "parallelism": f"head-sharded x{world}, no collective",
+                       "parallelism": (f"sequence-sharded x{world}: NCCL all-to-all in and out around "
+                                       f"head-sharded compute" if seq_layout
+                                       else f"head-sharded x{world}, no collective"),
                        "l2": "inputs larger than L2 (no flush needed)",
                        "flops_per_call": flops_total},
             "clocks": clocks,
@@ -337,6 +363,8 @@ def main():
     ap.add_argument("--workload", default="hunyuan_720p", choices=list(WORKLOADS))
     ap.add_argument("--cpu-blocks", type=int, default=384, help="query blocks per CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layout", default="head", choices=["head", "seq"],
+                    help="how inputs arrive at N > 1: head shards (no collective) or sequence shards")
     args = ap.parse_args()
     rank, local_rank, world = dist_env()
     spec = WORKLOADS[args.workload]
