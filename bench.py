@@ -346,7 +346,10 @@ def run_gpu(args, spec, rank, local_rank, world):
             "roofline": {"bound": "tensor", "kernel": "bsattn_fwd_kernel<128>", "achieved": attn_tflops,
                          "peak": peak, "unit": "TFLOP/s", "frac": attn_tflops / peak,
                          "peak_source": f"{pk['source']} sustained cuBLAS bf16 (kernel runs tens of ms)",
-                         "traffic": None},
+                         # DRAM bytes per launch: ncu capture of a small case (dram read 3.008 x and
+                         # write 0.796 x one tensor), scaled by the tensor size of this launch
+                         "traffic": 3.804 * tensor_bytes, "traffic_unit": "bytes",
+                         "algorithmic_flops": 4.0 * D * pairs_local},
             "cpu_baseline": cpu,
         }
         print(json.dumps(line), flush=True)

@@ -14,18 +14,16 @@
 //               issuing thread is an idle gap in its stream of MMAs; with two
 //               independent streams one fills the other's gaps and the pipe
 //               stays busy.
-//   warps 4-7   softmax of score columns 0..63, warps 8-11 of columns 64..127:
-//               warps w and w+4 own the same 32 query rows (TMEM lane
-//               quadrant) and split each row's 128 scores between them.  Per
-//               step: tcgen05.ld 64 scores, half-row maximum, exchange with the
-//               partner thread through shared memory (a 64-arrival mbarrier),
-//               exp2 in the log2 domain with packed fp32x2 arithmetic, P as
-//               packed bf16 to TMEM (tcgen05.st).  The accumulator O is
-//               rescaled in TMEM (each half its own columns) only when a row
-//               maximum grew by more than 2^8; sum and P use the same
-//               reference maximum, so the result is exact.  Epilogue:
-//               normalise, store bf16 rows, optionally through a row map
-//               (fused inverse permutation).
+//   warps 4-11  softmax: every warp owns 16 query rows and all 128 score columns
+//               (tcgen05.ld shape 16x256b: a row lives in four threads, so row
+//               maxima and sums are two shuffles and no warp depends on another).
+//               Per step: load the scores, row maxima, exp2 in the log2 domain
+//               with packed fp32x2 arithmetic, P as packed bf16 to TMEM
+//               (tcgen05.st shape 16x128b).  The accumulator O is rescaled in
+//               TMEM only when a row maximum grew by more than 2^8; sum and P
+//               use the same reference maximum, so the result is exact.
+//               Epilogue: normalise, store bf16 rows, optionally through a row
+//               map (fused inverse permutation).
 //   warp 3      idle (keeps the softmax warps aligned to TMEM lane quadrants).
 //
 // Shared memory (HD = 128): Q 32 KB + 3 x 32 KB K stages + 3 x 32 KB V stages.
@@ -57,10 +55,9 @@ struct SmemLayout {
   static constexpr int kKOff = kTileBytes;
   static constexpr int kVOff = kKOff + kStages * kTileBytes;
   static constexpr int kBarOff = kVOff + kStages * kTileBytes;
-  static constexpr int kNumBars = 1 + 4 * kStages + 2 + 2 + 2 + 4;
+  static constexpr int kNumBars = 1 + 4 * kStages + 2 + 2 + 2;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;      // tmem address + two give-up flags
-  static constexpr int kXchgOff = kMiscOff + 16;               // float [2][2][128] half-row exchange
-  static constexpr int kTotal = kXchgOff + 2 * 2 * 128 * 4;
+  static constexpr int kTotal = kMiscOff + 16;
 };
 
 struct Params {
@@ -138,11 +135,22 @@ __device__ __forceinline__ uint32_t cvt_bf16x2(float lo, float hi) {
   return d;
 }
 
+// Of the 16 column groups of a score tile, how many have their exp2 evaluated by the polynomial
+// on the FMA pipe instead of the special-function unit (measured: it pays off only for D = 64,
+// where the tensor work per tile is smaller and the special-function unit is the tighter limit).
+#ifndef DFS_POLY_GROUPS_D128
+#define DFS_POLY_GROUPS_D128 0
+#endif
+#ifndef DFS_POLY_GROUPS_D64
+#define DFS_POLY_GROUPS_D64 8
+#endif
+
 template <int HD>
 __global__ void __launch_bounds__(kThreads, 1)
     bsattn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const Params p) {
   using L = SmemLayout<HD>;
+  constexpr int kPolyGroups = HD == 128 ? DFS_POLY_GROUPS_D128 : DFS_POLY_GROUPS_D64;
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need 1024-byte alignment
     if (threadIdx.x == 0 && p.status) atomicExch(p.status, DFS_STATUS_BAD_SMEM_ALIGNMENT);
@@ -163,10 +171,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* s_full = v_empty + kStages;   // [2]  Q.K^T issuer -> softmax: scores of step j are in S[j&1]
   uint64_t* p_full = s_full + 2;          // [2]  softmax -> both issuers: P(j) is in P[j&1], S[j&1] is free
   uint64_t* mma_drain = p_full + 2;       // [2]  give-up path of the two issuers
-  uint64_t* pair_bar = mma_drain + 2;     // [4]  one per lane quadrant: the two warps that share its rows
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* xchg = reinterpret_cast<float*>(smem + L::kXchgOff);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -190,7 +196,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&p_full[b], 8);  // one arrival per softmax warp
       mbar_init(&mma_drain[b], 1);
     }
-    for (int qd = 0; qd < 4; ++qd) mbar_init(&pair_bar[qd], 64);
     abort_flag[0] = 0;  // set by the first wait that expires
     abort_flag[1] = 0;  // separate limit for the drain waits of the give-up path
     fence_barrier_init();
@@ -331,18 +336,23 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp >= 4) {
     // ------------------------------ softmax -------------------------------
-    const int half = (warp - 4) >> 2;                             // score columns [64*half, 64*half + 64)
+    // Warp w owns 16 query rows: TMEM lanes 32*(w%4) + 16*((w-4)/4) .. +15, all 128 score columns.
+    // In the 16x256b fragment a thread holds, for its two rows (a = lane/4, b = a + 8), the columns
+    // 8i + 2t and 8i + 2t + 1 (t = lane%4) of every group i of eight: a row lives in four threads,
+    // so row reductions are two shuffles and no other warp is involved.
     const int quad = warp & 3;
-    const int row = quad * 32 + lane;                             // TMEM lane = query row in the tile
-    const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
+    const int sub = (warp - 4) >> 2;
+    const int lane_base = quad * 32 + sub * 16;
+    const uint32_t lane_sel = static_cast<uint32_t>(lane_base) << 16;
+    const int t4 = lane & 3;
+    const int row_a = lane_base + (lane >> 2), row_b = row_a + 8;  // rows of the tile
     const float c = p.scale_log2;
     const uint64_t c2 = pack2(c, c);
-    float m_ref = -INFINITY;  // reference max (raw score units), identical in both halves of a row
-    uint64_t l2a = pack2(0.f, 0.f), l2b = l2a, l2c = l2a, l2d = l2a;  // eight partial sums of this half row
+    float m_a = -INFINITY, m_b = -INFINITY;  // reference maxima (raw score units) of the two rows
+    uint64_t la0 = pack2(0.f, 0.f), la1 = la0, lb0 = la0, lb1 = la0;  // partial row sums (this thread's columns)
     bool ok = true;
     const bool dump = p.debug != nullptr && qb == 0 && head == 0 && n_tiles > 0;
-    constexpr int kOCols = HD / 2;  // accumulator columns owned by this half
-    const uint32_t o_addr = tmem_base + lane_sel + kColO + half * kOCols;
+    const uint32_t o_addr = tmem_base + lane_sel + kColO;
     int kb_next = n_tiles > 0 ? (my_idx ? __ldg(my_idx) : 0) : 0;
 
     for (int j = 0; j < n_tiles; ++j) {
@@ -355,54 +365,55 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (!ok) break;
       tc_fence_after_sync();
 
-      uint32_t r0[32], r1[32];
-      const uint32_t s_addr = tmem_base + lane_sel + ((j & 1) ? kColS1 : kColS0) + half * 64;
-      tmem_ld32(s_addr, r0);
-      tmem_ld32(s_addr + 32, r1);
+      uint32_t r[64];
+      tmem_ld_16x256b_x16(tmem_base + lane_sel + ((j & 1) ? kColS1 : kColS0), r);
       tmem_wait_ld();
       if (valid < kBlockN) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (half * 64 + i >= valid) r0[i] = __float_as_uint(-INFINITY);
-          if (half * 64 + 32 + i >= valid) r1[i] = __float_as_uint(-INFINITY);
+        for (int i = 0; i < 16; ++i) {
+          const int col = 8 * i + 2 * t4;
+          if (col >= valid) r[4 * i] = r[4 * i + 2] = __float_as_uint(-INFINITY);
+          if (col + 1 >= valid) r[4 * i + 1] = r[4 * i + 3] = __float_as_uint(-INFINITY);
         }
       }
       if (dump && j == 0) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          p.debug[row * 128 + half * 64 + i] = __uint_as_float(r0[i]);
-          p.debug[row * 128 + half * 64 + 32 + i] = __uint_as_float(r1[i]);
+        for (int i = 0; i < 16; ++i) {
+          const int col = 8 * i + 2 * t4;
+          p.debug[row_a * 128 + col] = __uint_as_float(r[4 * i]);
+          p.debug[row_a * 128 + col + 1] = __uint_as_float(r[4 * i + 1]);
+          p.debug[row_b * 128 + col] = __uint_as_float(r[4 * i + 2]);
+          p.debug[row_b * 128 + col + 1] = __uint_as_float(r[4 * i + 3]);
         }
       }
 
-      // half-row maximum (four independent chains), then the row maximum via the partner thread
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      // row maxima: two independent chains per row over this thread's columns, then the row's 4 threads
+      float xa0 = -INFINITY, xa1 = -INFINITY, xb0 = -INFINITY, xb1 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 32; i += 4) {
-        mx0 = max3(mx0, __uint_as_float(r0[i]), __uint_as_float(r0[i + 1]));
-        mx1 = max3(mx1, __uint_as_float(r0[i + 2]), __uint_as_float(r0[i + 3]));
-        mx2 = max3(mx2, __uint_as_float(r1[i]), __uint_as_float(r1[i + 1]));
-        mx3 = max3(mx3, __uint_as_float(r1[i + 2]), __uint_as_float(r1[i + 3]));
+      for (int i = 0; i < 16; i += 2) {
+        xa0 = max3(xa0, __uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]));
+        xb0 = max3(xb0, __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+        xa1 = max3(xa1, __uint_as_float(r[4 * i + 4]), __uint_as_float(r[4 * i + 5]));
+        xb1 = max3(xb1, __uint_as_float(r[4 * i + 6]), __uint_as_float(r[4 * i + 7]));
       }
-      const float m_half = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      float* slot = xchg + (j & 1) * 256;  // [half][row], double-buffered by step parity
-      slot[half * 128 + row] = m_half;
-      mbar_arrive(&pair_bar[quad]);  // release: the partner sees the value after its wait
-      ok = mbar_wait_bounded(&pair_bar[quad], j & 1, abort_flag);
-      if (!ok) break;
-      const float m_tile = fmaxf(m_half, slot[(half ^ 1) * 128 + row]);
+      float mt_a = fmaxf(xa0, xa1), mt_b = fmaxf(xb0, xb1);
+      mt_a = fmaxf(mt_a, __shfl_xor_sync(0xffffffffu, mt_a, 1));
+      mt_b = fmaxf(mt_b, __shfl_xor_sync(0xffffffffu, mt_b, 1));
+      mt_a = fmaxf(mt_a, __shfl_xor_sync(0xffffffffu, mt_a, 2));
+      mt_b = fmaxf(mt_b, __shfl_xor_sync(0xffffffffu, mt_b, 2));
 
-      // both halves see the same m_tile and m_ref, so they take the same decision
-      const bool grow = (m_tile - m_ref) * c > kRescaleThreshold;  // also true for the first tile
-      if (__any_sync(0xffffffffu, grow)) {
-        const float m_new = fmaxf(m_ref, m_tile);
-        const float alpha = (m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_new) * c);
-        m_ref = m_new;
-        const uint64_t alpha2 = pack2(alpha, alpha), zero2 = pack2(0.f, 0.f);
-        l2a = fma2(l2a, alpha2, zero2);
-        l2b = fma2(l2b, alpha2, zero2);
-        l2c = fma2(l2c, alpha2, zero2);
-        l2d = fma2(l2d, alpha2, zero2);
+      const bool grow = (mt_a - m_a) * c > kRescaleThreshold || (mt_b - m_b) * c > kRescaleThreshold;
+      if (__any_sync(0xffffffffu, grow)) {  // also taken for the first tile
+        const float na = fmaxf(m_a, mt_a), nb = fmaxf(m_b, mt_b);
+        const float alpha_a = (m_a == -INFINITY) ? 0.f : ex2((m_a - na) * c);
+        const float alpha_b = (m_b == -INFINITY) ? 0.f : ex2((m_b - nb) * c);
+        m_a = na;
+        m_b = nb;
+        const uint64_t aa = pack2(alpha_a, alpha_a), ab = pack2(alpha_b, alpha_b), zero2 = pack2(0.f, 0.f);
+        la0 = fma2(la0, aa, zero2);
+        la1 = fma2(la1, aa, zero2);
+        lb0 = fma2(lb0, ab, zero2);
+        lb1 = fma2(lb1, ab, zero2);
         if (j > 0) {
           // P.V of step j-1 must have landed in O.  Its barrier completes one phase every
           // three steps and its next phase needs P(j+2), so the parity wait cannot be fooled.
@@ -410,100 +421,115 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (!ok) break;
           tc_fence_after_sync();
 #pragma unroll
-          for (int g = 0; g < kOCols / 32; ++g) {
+          for (int h = 0; h < HD / 64; ++h) {
             uint32_t o[32];
-            tmem_ld32(o_addr + g * 32, o);
+            tmem_ld_16x256b_x8(o_addr + h * 64, o);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(o_addr + g * 32, o);
+            for (int i = 0; i < 8; ++i) {
+              o[4 * i] = __float_as_uint(__uint_as_float(o[4 * i]) * alpha_a);
+              o[4 * i + 1] = __float_as_uint(__uint_as_float(o[4 * i + 1]) * alpha_a);
+              o[4 * i + 2] = __float_as_uint(__uint_as_float(o[4 * i + 2]) * alpha_b);
+              o[4 * i + 3] = __float_as_uint(__uint_as_float(o[4 * i + 3]) * alpha_b);
+            }
+            tmem_st_16x256b_x8(o_addr + h * 64, o);
           }
         }
       }
-      const float neg_mc = (m_ref == -INFINITY) ? 0.f : -m_ref * c;
-      const uint64_t neg_mc2 = pack2(neg_mc, neg_mc);
+      const float nma = (m_a == -INFINITY) ? 0.f : -m_a * c, nmb = (m_b == -INFINITY) ? 0.f : -m_b * c;
+      const uint64_t nma2 = pack2(nma, nma), nmb2 = pack2(nmb, nmb);
 
-      // P = exp2(S*c - m*c) as packed bf16
+      // P = exp2(S*c - m*c) as packed bf16: P column 4i + t of a row = keys 8i + 2t, 8i + 2t + 1
       uint32_t packed[32];
 #pragma unroll
-      for (int i = 0; i < 16; i += 2) {
-        // half of the exponentials on the special-function unit, half on the FMA pipe
-        float a0, a1, b0, b1, e0, e1, f0, f1;
-        unpack2(fma2(pack2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1])), c2, neg_mc2), a0, a1);
-        unpack2(fma2(pack2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1])), c2, neg_mc2), b0, b1);
-        a0 = ex2(a0);
-        a1 = ex2(a1);
-        b0 = ex2(b0);
-        b1 = ex2(b1);
-        exp2_poly2(fma2(pack2(__uint_as_float(r0[2 * i + 2]), __uint_as_float(r0[2 * i + 3])), c2, neg_mc2), e0, e1);
-        exp2_poly2(fma2(pack2(__uint_as_float(r1[2 * i + 2]), __uint_as_float(r1[2 * i + 3])), c2, neg_mc2), f0, f1);
-        l2a = add2(l2a, pack2(a0, a1));
-        l2b = add2(l2b, pack2(b0, b1));
-        l2c = add2(l2c, pack2(e0, e1));
-        l2d = add2(l2d, pack2(f0, f1));
-        packed[i] = cvt_bf16x2(a0, a1);            // keys 64*half + 2i, +1   (even key in the low half)
-        packed[16 + i] = cvt_bf16x2(b0, b1);       // keys 64*half + 32 + 2i, +1
-        packed[i + 1] = cvt_bf16x2(e0, e1);
-        packed[16 + i + 1] = cvt_bf16x2(f0, f1);
+      for (int i = 0; i < 16; ++i) {
+        const uint64_t xa = fma2(pack2(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1])), c2, nma2);
+        const uint64_t xb = fma2(pack2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), c2, nmb2);
+        float a0, a1, b0, b1;
+        if (i < kPolyGroups) {  // these groups on the FMA pipe
+          exp2_poly2(xa, a0, a1);
+          exp2_poly2(xb, b0, b1);
+        } else {
+          unpack2(xa, a0, a1);
+          unpack2(xb, b0, b1);
+          a0 = ex2(a0);
+          a1 = ex2(a1);
+          b0 = ex2(b0);
+          b1 = ex2(b1);
+        }
+        if (i & 1) {
+          la1 = add2(la1, pack2(a0, a1));
+          lb1 = add2(lb1, pack2(b0, b1));
+        } else {
+          la0 = add2(la0, pack2(a0, a1));
+          lb0 = add2(lb0, pack2(b0, b1));
+        }
+        packed[2 * i] = cvt_bf16x2(a0, a1);      // row a (even key in the low half)
+        packed[2 * i + 1] = cvt_bf16x2(b0, b1);  // row b
       }
-      tmem_st32(tmem_base + lane_sel + ((j & 1) ? kColP1 : kColP0) + half * 32, packed);
+      tmem_st_16x128b_x16(tmem_base + lane_sel + ((j & 1) ? kColP1 : kColP0), packed);
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[j & 1]);
     }
 
-    // row sum = this half + the partner's half (exchange buffer not used by the last step)
-    float l_lo, l_hi;
-    unpack2(add2(add2(l2a, l2b), add2(l2c, l2d)), l_lo, l_hi);
-    const float l_half = l_lo + l_hi;
-    float* slot = xchg + (n_tiles & 1) * 256;
-    slot[half * 128 + row] = l_half;
-    mbar_arrive(&pair_bar[quad]);
-    if (ok) ok = mbar_wait_bounded(&pair_bar[quad], n_tiles & 1, abort_flag);
-    const float l_sum = l_half + slot[(half ^ 1) * 128 + row];
+    // row sums: this thread's columns, then the row's four threads
+    float sa0, sa1, sb0, sb1;
+    unpack2(add2(la0, la1), sa0, sa1);
+    unpack2(add2(lb0, lb1), sb0, sb1);
+    float l_a = sa0 + sa1, l_b = sb0 + sb1;
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
 
     if (ok && n_tiles > 0)
       ok = mbar_wait_bounded(&v_empty[(n_tiles - 1) % kStages], ((n_tiles - 1) / kStages) & 1, abort_flag);
     if (ok) {
       tc_fence_after_sync();
-      const long long tok = static_cast<long long>(qb) * kBlockM + row;
-      const float inv_l = l_sum > 0.f ? 1.0f / l_sum : 0.f;
-      const bool live = tok < p.seq_len;  // a row with an empty list gets zeros
-      long long dst_row = tok;
-      if (live && p.out_row_map) dst_row = __ldg(p.out_row_map + tok);
-      __nv_bfloat16* dst =
-          p.out + (static_cast<size_t>(head) * p.seq_len + (live ? dst_row : 0)) * HD + half * kOCols;
+      const float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+      const long long tok_a = static_cast<long long>(qb) * kBlockM + row_a, tok_b = tok_a + 8;
+      const bool live_a = tok_a < p.seq_len, live_b = tok_b < p.seq_len;  // a row with an empty list gets zeros
+      long long dst_a = tok_a, dst_b = tok_b;
+      if (p.out_row_map) {
+        if (live_a) dst_a = __ldg(p.out_row_map + tok_a);
+        if (live_b) dst_b = __ldg(p.out_row_map + tok_b);
+      }
+      __nv_bfloat16* out_a = p.out + (static_cast<size_t>(head) * p.seq_len + (live_a ? dst_a : 0)) * HD;
+      __nv_bfloat16* out_b = p.out + (static_cast<size_t>(head) * p.seq_len + (live_b ? dst_b : 0)) * HD;
 #pragma unroll
-      for (int g = 0; g < kOCols / 32; ++g) {
+      for (int h = 0; h < HD / 64; ++h) {
         uint32_t o[32];
         if (n_tiles > 0) {
-          tmem_ld32(o_addr + g * 32, o);
+          tmem_ld_16x256b_x8(o_addr + h * 64, o);
           tmem_wait_ld();
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = 0u;
         }
-        if (dump) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            p.debug[128 * 128 + row * HD + half * kOCols + g * 32 + i] = __uint_as_float(o[i]);
-        }
-        if (live) {
-#pragma unroll
-          for (int v8 = 0; v8 < 4; ++v8) {
-            uint4 pk;
-            pk.x = cvt_bf16x2(__uint_as_float(o[v8 * 8 + 0]) * inv_l, __uint_as_float(o[v8 * 8 + 1]) * inv_l);
-            pk.y = cvt_bf16x2(__uint_as_float(o[v8 * 8 + 2]) * inv_l, __uint_as_float(o[v8 * 8 + 3]) * inv_l);
-            pk.z = cvt_bf16x2(__uint_as_float(o[v8 * 8 + 4]) * inv_l, __uint_as_float(o[v8 * 8 + 5]) * inv_l);
-            pk.w = cvt_bf16x2(__uint_as_float(o[v8 * 8 + 6]) * inv_l, __uint_as_float(o[v8 * 8 + 7]) * inv_l);
-            reinterpret_cast<uint4*>(dst + g * 32)[v8] = pk;
+        for (int i = 0; i < 8; ++i) {
+          const int col = h * 64 + 8 * i + 2 * t4;
+          if (dump) {
+            p.debug[128 * 128 + row_a * HD + col] = __uint_as_float(o[4 * i]);
+            p.debug[128 * 128 + row_a * HD + col + 1] = __uint_as_float(o[4 * i + 1]);
+            p.debug[128 * 128 + row_b * HD + col] = __uint_as_float(o[4 * i + 2]);
+            p.debug[128 * 128 + row_b * HD + col + 1] = __uint_as_float(o[4 * i + 3]);
           }
+          if (live_a)
+            *reinterpret_cast<uint32_t*>(out_a + col) =
+                cvt_bf16x2(__uint_as_float(o[4 * i]) * inv_a, __uint_as_float(o[4 * i + 1]) * inv_a);
+          if (live_b)
+            *reinterpret_cast<uint32_t*>(out_b + col) =
+                cvt_bf16x2(__uint_as_float(o[4 * i + 2]) * inv_b, __uint_as_float(o[4 * i + 3]) * inv_b);
         }
       }
-      if (dump && half == 0) {
-        p.debug[128 * 128 + 128 * HD + row] = l_sum;
-        p.debug[128 * 128 + 128 * HD + 128 + row] = m_ref;
+      if (dump && t4 == 0) {
+        p.debug[128 * 128 + 128 * HD + row_a] = l_a;
+        p.debug[128 * 128 + 128 * HD + row_b] = l_b;
+        p.debug[128 * 128 + 128 * HD + 128 + row_a] = m_a;
+        p.debug[128 * 128 + 128 * HD + 128 + row_b] = m_b;
       }
     }
   }
