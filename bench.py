@@ -303,11 +303,23 @@ def run_gpu(args, spec, rank, local_rank, world):
     hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
     dq, dk, dv = (torch.empty_like(t) for t in step_inputs)
 
+    from dfsattn_b200.host_io import dfs_attention_host
+    host_kw = dict(skip_steps=12, cache_interval=12, sparsity=spec["sparsity"], sparsity_dcrt=0.1,
+                   tile_size=16, block_size=128, video_perm=vperm)
+    if hy:
+        host_kw.update(step_idx=12, video_len=video_len)
+    else:
+        host_kw.update(step_idx=24)
+
     def e2e_step():
-        dq.copy_(hq, non_blocking=True)
-        dk.copy_(hk, non_blocking=True)
-        dv.copy_(hv, non_blocking=True)
-        hout.copy_(call(dq, dk, dv), non_blocking=True)
+        if seq_layout:  # sequence shards: upload, swap, compute, swap back, download
+            dq.copy_(hq, non_blocking=True)
+            dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True)
+            hout.copy_(call(dq, dk, dv), non_blocking=True)
+        else:           # the host-buffer entry point: copies of head groups overlap the kernels
+            dfs_attention_host(hq, hk, hv, out=hout, head_groups=4, device=dev,
+                               flavor="hyvideo" if hy else "wan", layer_idx=1000, **host_kw)
 
     e2e_step()
     n_e2e = max(2, min(args.steps, 5))

@@ -194,3 +194,22 @@ def test_wan_processor_gate_and_counter():
     with pytest.raises(ValueError):
         Wan_DFSAttn_Processor2_0("dfs", 0.5, 16, 128, None, 1, [0], 1, 1, 0.1, True, False,
                                  sparse_execution="flex64")
+
+
+def test_host_buffer_entry_point_matches_device_call():
+    from dfsattn_b200.attention_hyvideo import dfs_attention
+    from dfsattn_b200.host_io import dfs_attention_host
+    name = "hy_text_5x11x17_t256"
+    spec = CASES[name]
+    q, k, v, vperm = inputs(name)
+    L = q.shape[2]
+    kw = dict(step_idx=12, skip_steps=12, cache_interval=12, sparsity=spec["sparsity"], sparsity_dcrt=0.1,
+              tile_size=16, block_size=128, video_len=L - spec["text"], video_perm=vperm)
+    qh, kh, vh = (t.bfloat16().pin_memory() for t in (q, k, v))
+    want = dfs_attention(qh.cuda(), kh.cuda(), vh.cuda(), layer_idx=5, **kw).cpu()
+    got = dfs_attention_host(qh, kh, vh, head_groups=2, layer_idx=6, **kw)
+    torch.cuda.synchronize()
+    assert got.is_pinned() and got.shape == want.shape
+    assert torch.equal(got, want)       # heads are independent: grouping them changes nothing
+    with pytest.raises(ValueError):
+        dfs_attention_host(qh.cuda(), kh.cuda(), vh.cuda(), **kw)
