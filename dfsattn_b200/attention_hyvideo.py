@@ -41,8 +41,8 @@ def _reject_unsupported(sparse_execution, selector_mode, block_top_p, token_top_
         raise ValueError("token_top_k > 0 (residual tokens) is not supported")
     if block_size != 128:
         raise ValueError("block_size must be 128")
-    if tile_size != 16:
-        raise ValueError("tile_size must be 16")
+    if tile_size not in (16, 32, 64):
+        raise ValueError("tile_size must be 16, 32 or 64")
 
 
 class DFS_Attention(nn.Module):

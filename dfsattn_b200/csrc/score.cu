@@ -27,15 +27,16 @@ namespace {
 
 using namespace dfs;
 
-constexpr int kTile = 16;    // tokens per pooled tile
-constexpr int kBlock = 128;  // tokens per block
-constexpr int kTilesPerBlock = kBlock / kTile;
-constexpr int kGemmTile = 128;  // pooled rows / columns per MMA tile (= 16 blocks)
+constexpr int kBlock = 128;     // tokens per block
+constexpr int kGemmTile = 128;  // pooled rows / columns per MMA tile
+// tokens per pooled tile: 16, 32 or 64 (8, 4 or 2 tiles per block)
 
 struct ScoreShape {
   int heads;
   long long seq_len, video_len;
   int head_dim;
+  int tile;      // tokens per pooled tile
+  int tpb;       // pooled tiles per block
   int q_blocks;  // rows of the block-score matrix
   int k_blocks;
   int nq, nk;          // pooled tiles (q_blocks*8, k_blocks*8)
@@ -43,16 +44,19 @@ struct ScoreShape {
   long long video_padded;  // Vb*128: scoring position where the text part starts
 };
 
-__host__ ScoreShape make_shape(int heads, int64_t seq_len, int64_t video_len, int head_dim, int wan_layout) {
+__host__ ScoreShape make_shape(int heads, int64_t seq_len, int64_t video_len, int head_dim, int tile,
+                               int wan_layout) {
   ScoreShape s;
+  s.tile = tile;
+  s.tpb = kBlock / tile;
   s.heads = heads;
   s.seq_len = seq_len;
   s.video_len = wan_layout ? seq_len : video_len;
   s.head_dim = head_dim;
   s.k_blocks = static_cast<int>((seq_len + kBlock - 1) / kBlock);
   s.q_blocks = static_cast<int>((s.video_len + kBlock - 1) / kBlock);
-  s.nq = s.q_blocks * kTilesPerBlock;
-  s.nk = s.k_blocks * kTilesPerBlock;
+  s.nq = s.q_blocks * s.tpb;
+  s.nk = s.k_blocks * s.tpb;
   s.nq_pad = (s.nq + kGemmTile - 1) / kGemmTile * kGemmTile;
   s.nk_pad = (s.nk + kGemmTile - 1) / kGemmTile * kGemmTile;
   s.video_padded = static_cast<long long>(s.q_blocks) * kBlock;
@@ -110,7 +114,7 @@ struct Vec16<float> {
   }
 };
 
-// One thread: one 16-byte column chunk of one pooled tile (16 rows summed in fp32), written as
+// One thread: one 16-byte column chunk of one pooled tile (its rows summed in fp32), written as
 // bf16 hi / lo rows.  Padding tiles are written as zeros.
 template <typename T>
 __global__ void __launch_bounds__(256) pool_tiles_kernel(const T* __restrict__ q, const T* __restrict__ k,
@@ -135,9 +139,9 @@ __global__ void __launch_bounds__(256) pool_tiles_kernel(const T* __restrict__ q
 #pragma unroll
   for (int i = 0; i < E; ++i) acc[i] = 0.f;
   if (tile < n_tiles) {
-    const long long p0 = static_cast<long long>(tile) * kTile;
+    const long long p0 = static_cast<long long>(tile) * s.tile;
 #pragma unroll 4
-    for (int r = 0; r < kTile; ++r) {
+    for (int r = 0; r < s.tile; ++r) {
       const long long row = scoring_row(p0 + r, s.video_len, s.video_padded, s.seq_len);
       if (row >= 0) {
         const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + row * s.head_dim) + ch);
@@ -148,7 +152,7 @@ __global__ void __launch_bounds__(256) pool_tiles_kernel(const T* __restrict__ q
   __nv_bfloat16 hi[E], lo[E];
 #pragma unroll
   for (int i = 0; i < E; ++i) {
-    const float mean = acc[i] * (1.0f / kTile);
+    const float mean = acc[i] / static_cast<float>(s.tile);  // exact: the tile size is a power of two
     hi[i] = __float2bfloat16_rn(mean);
     lo[i] = __float2bfloat16_rn(mean - __bfloat162float(hi[i]));
   }
@@ -198,7 +202,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-template <int HD>
+template <int HD, int TPB>
 __global__ void __launch_bounds__(kLseThreads, 1)
     tile_lse_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     float* __restrict__ lse, ScoreShape s, float scale_log2, int32_t* status) {
@@ -327,18 +331,18 @@ __global__ void __launch_bounds__(kLseThreads, 1)
         tmem_ld32(tmem_base + lane_sel + b * 128 + g * 32, r);
         tmem_wait_ld();
 #pragma unroll
-        for (int grp = 0; grp < 4; ++grp) {
-          float v[8];
+        for (int grp = 0; grp < 32 / TPB; ++grp) {  // one key block = TPB consecutive pooled columns
+          float v[TPB];
           float m = -INFINITY;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            v[i] = __uint_as_float(r[grp * 8 + i]) * scale_log2;
+          for (int i = 0; i < TPB; ++i) {
+            v[i] = __uint_as_float(r[grp * TPB + i]) * scale_log2;
             m = fmaxf(m, v[i]);
           }
           float sum = 0.f;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) sum += ex2_approx(v[i] - m);
-          const int kb = ct * (kGemmTile / kTilesPerBlock) + g * 4 + grp;
+          for (int i = 0; i < TPB; ++i) sum += ex2_approx(v[i] - m);
+          const int kb = ct * (kGemmTile / TPB) + g * (32 / TPB) + grp;
           if (row < s.nq && kb < s.k_blocks) out_row[kb] = m + lg2_approx(sum);
         }
       }
@@ -358,16 +362,16 @@ __global__ void __launch_bounds__(kLseThreads, 1)
   }
 }
 
-// One CTA per (query block, head): 8 pooled rows x Kb stored base-2 LSEs -> Kb block scores.
+// One CTA per (query block, head): its pooled rows (at most 8) x Kb stored base-2 LSEs -> Kb block scores.
 __global__ void __launch_bounds__(256) block_sum_kernel(const float* __restrict__ lse,
                                                         float* __restrict__ block_scores, ScoreShape s) {
-  __shared__ float row_max[kTilesPerBlock];
-  __shared__ float row_inv[kTilesPerBlock];
+  __shared__ float row_max[8];
+  __shared__ float row_inv[8];
   const int head = blockIdx.y;
   const int qb = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const float* __restrict__ rows = lse + (static_cast<size_t>(head) * s.nq + qb * kTilesPerBlock) * s.k_blocks;
-  {
+  const float* __restrict__ rows = lse + (static_cast<size_t>(head) * s.nq + qb * s.tpb) * s.k_blocks;
+  if (warp < s.tpb) {
     const float* __restrict__ r = rows + static_cast<size_t>(warp) * s.k_blocks;  // warp i <-> pooled row i
     float m = -INFINITY;
     for (int c = lane; c < s.k_blocks; c += 32) m = fmaxf(m, r[c]);
@@ -386,8 +390,7 @@ __global__ void __launch_bounds__(256) block_sum_kernel(const float* __restrict_
   float* __restrict__ out = block_scores + (static_cast<size_t>(head) * s.q_blocks + qb) * s.k_blocks;
   for (int c = threadIdx.x; c < s.k_blocks; c += blockDim.x) {
     float b = 0.f;
-#pragma unroll
-    for (int i = 0; i < kTilesPerBlock; ++i)
+    for (int i = 0; i < s.tpb; ++i)
       b += exp2f(rows[static_cast<size_t>(i) * s.k_blocks + c] - row_max[i]) * row_inv[i];
     out[c] = b;
   }
@@ -404,7 +407,7 @@ int launch_pool(const void* q, const void* k, __nv_bfloat16* qm, __nv_bfloat16* 
   return static_cast<int>(cudaGetLastError());
 }
 
-template <int HD>
+template <int HD, int TPB>
 int launch_lse(const __nv_bfloat16* qm, const __nv_bfloat16* km, float* lse, const ScoreShape& s, float scale_log2,
                int32_t* status, cudaStream_t stream) {
   using L = LseSmem<HD>;
@@ -412,15 +415,16 @@ int launch_lse(const __nv_bfloat16* qm, const __nv_bfloat16* km, float* lse, con
   int rc = dfs_make_bf16_tile_map(&mq, qm, 2 * s.heads, s.nq_pad, HD);
   if (rc == 0) rc = dfs_make_bf16_tile_map(&mk, km, 2 * s.heads, s.nk_pad, HD);
   if (rc != 0) return rc;
-  DFS_CUDA_CHECK(cudaFuncSetAttribute(tile_lse_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  DFS_CUDA_CHECK(
+      cudaFuncSetAttribute(tile_lse_kernel<HD, TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
   dim3 grid(s.nq_pad / kGemmTile, s.heads);
-  tile_lse_kernel<HD><<<grid, kLseThreads, L::kTotal, stream>>>(mq, mk, lse, s, scale_log2, status);
+  tile_lse_kernel<HD, TPB><<<grid, kLseThreads, L::kTotal, stream>>>(mq, mk, lse, s, scale_log2, status);
   return static_cast<int>(cudaGetLastError());
 }
 
 int check_shape(int heads, int64_t seq_len, int64_t video_len, int head_dim, int tile, int block,
                 int wan_layout) {
-  if (tile != kTile || block != kBlock) return DFS_ERR_SHAPE;
+  if (block != kBlock || (tile != 16 && tile != 32 && tile != 64)) return DFS_ERR_SHAPE;
   if (head_dim != 64 && head_dim != 128) return DFS_ERR_SHAPE;
   if (heads <= 0 || heads > 32767 || seq_len <= 0) return DFS_ERR_SHAPE;
   if (!wan_layout) {
@@ -444,8 +448,14 @@ int run_block_scores(const void* q_perm, const void* k_perm, int dtype, const Sc
                                     : launch_pool<float>(q_perm, k_perm, qm, km, s, stream);
   if (err != 0) return err;
   const float scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(s.head_dim));
-  err = s.head_dim == 128 ? launch_lse<128>(qm, km, lse, s, scale_log2, status, stream)
-                          : launch_lse<64>(qm, km, lse, s, scale_log2, status, stream);
+  if (s.head_dim == 128)
+    err = s.tpb == 8   ? launch_lse<128, 8>(qm, km, lse, s, scale_log2, status, stream)
+          : s.tpb == 4 ? launch_lse<128, 4>(qm, km, lse, s, scale_log2, status, stream)
+                       : launch_lse<128, 2>(qm, km, lse, s, scale_log2, status, stream);
+  else
+    err = s.tpb == 8   ? launch_lse<64, 8>(qm, km, lse, s, scale_log2, status, stream)
+          : s.tpb == 4 ? launch_lse<64, 4>(qm, km, lse, s, scale_log2, status, stream)
+                       : launch_lse<64, 2>(qm, km, lse, s, scale_log2, status, stream);
   if (err != 0) return err;
   dim3 grid(s.q_blocks, s.heads);
   block_sum_kernel<<<grid, 256, 0, stream>>>(lse, block_scores, s);
@@ -458,7 +468,7 @@ extern "C" int64_t dfs_score_workspace_bytes(int heads, int64_t seq_len, int64_t
                                              int tile, int block, int wan_layout) {
   const int rc = check_shape(heads, seq_len, video_len, head_dim, tile, block, wan_layout);
   if (rc != 0) return rc;
-  return static_cast<int64_t>(make_workspace(make_shape(heads, seq_len, video_len, head_dim, wan_layout)).total);
+  return static_cast<int64_t>(make_workspace(make_shape(heads, seq_len, video_len, head_dim, tile, wan_layout)).total);
 }
 
 extern "C" int dfs_block_scores(const void* q_perm, const void* k_perm, int dtype, int heads, int64_t seq_len,
@@ -472,7 +482,7 @@ extern "C" int dfs_block_scores(const void* q_perm, const void* k_perm, int dtyp
   if (dtype != DFS_DTYPE_BF16 && dtype != DFS_DTYPE_F32) return DFS_ERR_DTYPE;
   const int rc = check_shape(heads, seq_len, video_len, head_dim, tile, block, wan_layout);
   if (rc != 0) return rc;
-  const ScoreShape s = make_shape(heads, seq_len, video_len, head_dim, wan_layout);
+  const ScoreShape s = make_shape(heads, seq_len, video_len, head_dim, tile, wan_layout);
   const Workspace w = make_workspace(s);
   if (workspace_bytes < static_cast<int64_t>(w.total)) return DFS_ERR_WORKSPACE;
   return run_block_scores(q_perm, k_perm, dtype, s, block_scores, static_cast<char*>(workspace), status,
@@ -528,7 +538,7 @@ extern "C" int dfs_block_scores_static(const void* q_perm, const void* k_perm, i
   if (dtype != DFS_DTYPE_BF16 && dtype != DFS_DTYPE_F32) return DFS_ERR_DTYPE;
   const int rc = check_shape(heads, seq_len, video_len, head_dim, tile, block, wan_layout);
   if (rc != 0) return rc;
-  const ScoreShape s = make_shape(heads, seq_len, video_len, head_dim, wan_layout);
+  const ScoreShape s = make_shape(heads, seq_len, video_len, head_dim, tile, wan_layout);
   const Workspace w = make_workspace(s);
   if (w.total > kStaticScratchBytes) return DFS_ERR_STATIC_SCRATCH;  // shape needs more than the fixed array
   char* base = nullptr;

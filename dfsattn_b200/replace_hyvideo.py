@@ -40,8 +40,8 @@ class HunyuanVideo_DFSAttn_Processor2_0:
                 raise ValueError(f"sparse_execution={sparse_execution!r}: only 'native' is built for B200")
             if selector_mode != "topk" or block_top_p is not None or token_top_k:
                 raise ValueError("only the top-k block selector is built for B200")
-            if block_size != 128 or tile_size != 16:
-                raise ValueError("block_size must be 128 and tile_size 16")
+            if block_size != 128 or tile_size not in (16, 32, 64):
+                raise ValueError("block_size must be 128 and tile_size 16, 32 or 64")
         for name in other_backend_knobs:
             if not (name.startswith("flashinfer64_") or name.startswith("attention_debug_")):
                 raise TypeError(f"unexpected keyword argument {name!r}")

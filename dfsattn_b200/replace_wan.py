@@ -32,8 +32,8 @@ class Wan_DFSAttn_Processor2_0:
         if mode == "dfs" and not cross_flag:
             if sparse_execution != "native":
                 raise ValueError(f"sparse_execution={sparse_execution!r}: only 'native' is built for B200")
-            if block_size != 128 or tile_size != 16:
-                raise ValueError("block_size must be 128 and tile_size 16")
+            if block_size != 128 or tile_size not in (16, 32, 64):
+                raise ValueError("block_size must be 128 and tile_size 16, 32 or 64")
         for name in other_backend_knobs:
             if not name.startswith("flashinfer64_"):
                 raise TypeError(f"unexpected keyword argument {name!r}")

@@ -106,7 +106,7 @@ int64_t dfs_score_workspace_bytes(int heads, int64_t seq_len, int64_t video_len,
  * end only, query tiles cover everything).  q, k are the PERMUTED tensors
  * [H, L, D] (bf16 or f32).  Means are fp32, carried into the tensor-core
  * product as a bf16 hi + lo pair (16 significant bits), logits accumulate in
- * fp32, softmax and sums are fp32.  tile must be 16 and block 128; workspace
+ * fp32, softmax and sums are fp32.  tile is 16, 32 or 64 and block 128; workspace
  * 256-byte aligned; status: device int32, zero-initialised by the caller. */
 int dfs_block_scores(const void* q_perm, const void* k_perm, int dtype, int heads,
                      int64_t seq_len, int64_t video_len, int head_dim, int tile, int block,

@@ -91,4 +91,4 @@ def test_processor_constructors_keep_the_reference_argument_order():
         with pytest.raises(ValueError):
             HP("dfs", 0.3, 16, 128, 1024, None, 5, [0], 12, 12, 0.1, True, **bad)
     with pytest.raises(ValueError):
-        HP("dfs", 0.3, 32, 128, 1024, None, 5, [0], 12, 12, 0.1, True)
+        HP("dfs", 0.3, 8, 128, 1024, None, 5, [0], 12, 12, 0.1, True)   # tile sizes: 16, 32, 64

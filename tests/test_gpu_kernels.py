@@ -153,10 +153,33 @@ def test_block_scores_and_lists_match_reference(ops, name, dtype):
                 assert abs(float(want[h, r, c] - kth)) <= 2e-4 * float(kth)
 
 
+@pytest.mark.parametrize("tile", [32, 64])
+@pytest.mark.parametrize("name", ["hy_text_5x11x17_t256", "ragged_5x11x17"])
+def test_block_scores_other_tile_sizes(ops, name, tile):
+    """tile_size 32 and 64 (4 and 2 pooled tiles per block) against the oracle."""
+    from dfsattn_b200 import engine
+    spec = CASES[name]
+    q, k, v, vperm = inputs(name)
+    L = q.shape[2]
+    video_len = L - spec["text"]
+    perm, _ = oracle.build_permutation(vperm, L, video_len)
+    q, k = q.bfloat16(), k.bfloat16()
+    qp = q[0][:, perm].contiguous().cuda()
+    kp = k[0][:, perm].contiguous().cuda()
+    got = ops.block_scores(qp, kp, video_len, False, tile=tile).cpu()
+    want = oracle.block_scores_hyvideo(q.float(), k.float(), perm, video_len, tile=tile)[0]
+    torch.testing.assert_close(got, want, rtol=2e-4, atol=1e-6)
+    tpb = 128 // tile
+    torch.testing.assert_close(got.sum(-1), torch.full_like(got.sum(-1), float(tpb)), rtol=1e-4, atol=1e-4)
+    lists = engine.compute_block_lists(qp, kp, video_len, spec["sparsity"], "hyvideo", tile=tile)
+    ref = oracle.dfs.select_hyvideo(want[None], L, video_len, spec["sparsity"])
+    assert (lists.to_bool_mask().cpu() != ref).sum() <= 2
+
+
 def test_block_scores_rejects_bad_shapes(ops):
     x = torch.zeros(1, 256, 128, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(ValueError):
-        ops.block_scores(x, x, 256, True, tile=32)
+        ops.block_scores(x, x, 256, True, tile=8)
     with pytest.raises(ValueError):
         ops.block_scores(x, x, 129, False)  # [video | gap | text] does not fit in Kb blocks
     with pytest.raises(ValueError):

@@ -116,7 +116,7 @@ def test_unsupported_knobs_raise():
     from dfsattn_b200.attention_hyvideo import dfs_attention
     x = torch.zeros(1, 1, 128, 128, device="cuda", dtype=torch.bfloat16)
     for bad in (dict(sparse_execution="hybrid"), dict(selector_mode="kp"), dict(block_top_p=0.5),
-                dict(token_top_k=4), dict(block_size=64), dict(tile_size=32)):
+                dict(token_top_k=4), dict(block_size=64), dict(tile_size=8)):
         kw = dict(tile_size=16, video_len=128)
         kw.update(bad)
         with pytest.raises(ValueError):
