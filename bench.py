@@ -120,7 +120,8 @@ def cpu_sample(spec, budget_blocks):
                              device="cpu", seed=0, head_offset=0, total_heads=1)
     L = q.shape[2]
     video_len = L - spec["text"]
-    vperm = torch.from_numpy(oracle.hilbert3d_perm(f, h, w))
+    vperm = torch.from_numpy(oracle.hilbert3d_perm(f, h, w)) if spec.get("order", "hilbert3d") == "hilbert3d" \
+        else None
     perm, inv = oracle.build_permutation(vperm, L, video_len)
     t0 = time.perf_counter()
     if spec["flavor"] == "hyvideo":
@@ -174,8 +175,11 @@ def run_reference(args, spec, rank, world):
 # --------------------------------------------------------------------------- #
 # GPU arm
 # --------------------------------------------------------------------------- #
-def timed(fn, steps, barrier):
-    """CUDA-event time of `steps` calls on the current stream, bracketed by barrier + synchronize."""
+def timed(fn, steps, barrier, warm=0):
+    """CUDA-event time of `steps` calls on the current stream, bracketed by barrier + synchronize;
+    `warm` untimed calls first (they let torch's allocator settle)."""
+    for _ in range(warm):
+        fn()
     barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -234,7 +238,7 @@ def run_gpu(args, spec, rank, local_rank, world):
                                  device=dev, seed=0, head_offset=rank * h_local, total_heads=H)
     L = q.shape[2]
     video_len = L - spec["text"]
-    vperm = hilbert3d_perm(f, h, w)
+    vperm = hilbert3d_perm(f, h, w) if spec.get("order", "hilbert3d") == "hilbert3d" else None
     hy = spec["flavor"] == "hyvideo"
     Attn = HyAttn if hy else WanAttn
 
@@ -279,20 +283,25 @@ def run_gpu(args, spec, rank, local_rank, world):
     # ---- per-stage device times (same inputs, same stream) -----------------
     perm, _ = engine._perm_cache.get(vperm, L, video_len, dev)
     qh, kh, vh = q[0], k[0], v[0]
-    qp, kp, vp = ops.permute_qkv(qh, kh, vh, perm)
     n_stage = max(3, min(args.steps, 10))
-    t_perm = timed(lambda: ops.permute_qkv(qh, kh, vh, perm), n_stage, barrier) / n_stage
+    if perm is not None:
+        qp, kp, vp = ops.permute_qkv(qh, kh, vh, perm)
+        t_perm = timed(lambda: ops.permute_qkv(qh, kh, vh, perm), n_stage, barrier, warm=2) / n_stage
+    else:  # raster order: no gather at all
+        qp, kp, vp = qh.contiguous(), kh.contiguous(), vh.contiguous()
+        t_perm = float("nan")
     t_score = timed(lambda: engine.compute_block_lists(qp, kp, video_len, spec["sparsity"], spec["flavor"]),
-                    n_stage, barrier) / n_stage
+                    n_stage, barrier, warm=1) / n_stage
     out_buf = torch.empty_like(qp)
     t_attn = timed(lambda: ops.block_sparse_fwd(qp, kp, vp, lists.idx, lists.cnt, out_row_map=perm, out=out_buf),
-                   n_stage, barrier) / n_stage
+                   n_stage, barrier, warm=1) / n_stage
     t_attn = reduce(t_attn, dist.ReduceOp.MAX if world > 1 else None)
     pk = peaks()
     attn_tflops = 4.0 * D * pairs_local / t_attn / 1e12          # this rank's kernel
     tensor_bytes = h_local * L * D * 2
     stages = {
-        "permute_ms": 1e3 * t_perm, "permute_gbs": 6 * tensor_bytes / t_perm / 1e9,
+        "permute_ms": None if perm is None else 1e3 * t_perm,
+        "permute_gbs": None if perm is None else 6 * tensor_bytes / t_perm / 1e9,
         "score_select_ms": 1e3 * t_score,
         "score_select_gbs_algorithmic": (2 * tensor_bytes + lists.idx.numel() * 4) / t_score / 1e9,
         "attention_ms": 1e3 * t_attn,
@@ -321,9 +330,8 @@ def run_gpu(args, spec, rank, local_rank, world):
             dfs_attention_host(hq, hk, hv, out=hout, head_groups=4, device=dev,
                                flavor="hyvideo" if hy else "wan", layer_idx=1000, **host_kw)
 
-    e2e_step()
     n_e2e = max(2, min(args.steps, 5))
-    e_secs = timed(e2e_step, n_e2e, barrier) / n_e2e
+    e_secs = timed(e2e_step, n_e2e, barrier, warm=2) / n_e2e
     e_secs = reduce(e_secs, dist.ReduceOp.MAX if world > 1 else None)
     ops.check_status(dev)
     e2e = {"value": flops_total / e_secs / 1e12, "unit": UNIT, "ms_per_call": 1e3 * e_secs,
@@ -344,7 +352,8 @@ def run_gpu(args, spec, rank, local_rank, world):
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "grid": list(spec["grid"]), "text_tokens": spec["text"],
                        "seq_len": L, "heads": H, "heads_per_gpu": h_local, "head_dim": D,
-                       "sparsity": spec["sparsity"], "order": "hilbert3d", "block": 128, "tile": 16,
+                       "sparsity": spec["sparsity"], "order": spec.get("order", "hilbert3d"), "block": 128,
+                       "tile": 16,
                        "step": "refresh call: permute + score + select + attention (+fused unpermute)",
                        "parallelism": (f"sequence-sharded x{world}: NCCL all-to-all in and out around "
                                        f"head-sharded compute" if seq_layout
@@ -378,11 +387,17 @@ def main():
     ap.add_argument("--workload", default="hunyuan_720p", choices=list(WORKLOADS))
     ap.add_argument("--cpu-blocks", type=int, default=384, help="query blocks per CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sparsity", type=float, default=None, help="override the workload's sparsity")
+    ap.add_argument("--order", default="hilbert3d", choices=["hilbert3d", "org"],
+                    help="token order: 3-D Hilbert curve or raster (no permutation)")
     ap.add_argument("--layout", default="head", choices=["head", "seq"],
                     help="how inputs arrive at N > 1: head shards (no collective) or sequence shards")
     args = ap.parse_args()
     rank, local_rank, world = dist_env()
-    spec = WORKLOADS[args.workload]
+    spec = dict(WORKLOADS[args.workload])
+    if args.sparsity is not None:
+        spec["sparsity"] = args.sparsity
+    spec["order"] = args.order
     if args.impl == "reference":
         run_reference(args, spec, rank, world)
         return
