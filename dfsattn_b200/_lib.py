@@ -33,6 +33,12 @@ SIGNATURES = {
                                 c_void_p, c_int, c_void_p, c_void_p]),
     "dfs_block_sparse_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                      c_void_p, c_int, c_int64, c_int64, c_int, c_float, c_void_p, c_void_p]),
+    "dfs_block_sparse_fwd_ex": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                        c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_float, c_void_p,
+                                        c_void_p]),
+    "dfs_qkv_prepare": (c_int, [c_void_p] * 5 + [c_float, c_float, c_int, c_void_p, c_void_p, c_int, c_int64,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int,
+                                c_void_p]),
 }
 
 # testing hooks exported by the library but not part of the public header

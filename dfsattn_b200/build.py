@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libdfs_b200.so")
-SOURCES = ["permute.cu", "score.cu", "select.cu", "attn_fwd.cu", "host.cpp"]
+SOURCES = ["permute.cu", "prepare.cu", "score.cu", "select.cu", "attn_fwd.cu", "host.cpp"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

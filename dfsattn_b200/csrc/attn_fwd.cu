@@ -69,6 +69,8 @@ struct Params {
   float* debug;         // optional dump for (query block 0, head 0): S of the first tile, O, l, m
   long long seq_len;
   long long kv_len;
+  long long out_head_stride;   // elements between heads of the output
+  long long out_token_stride;  // elements between tokens of the output
   int kmax;
   int q_blocks, k_blocks;
   float scale_log2;
@@ -496,8 +498,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (live_a) dst_a = __ldg(p.out_row_map + tok_a);
         if (live_b) dst_b = __ldg(p.out_row_map + tok_b);
       }
-      __nv_bfloat16* out_a = p.out + (static_cast<size_t>(head) * p.seq_len + (live_a ? dst_a : 0)) * HD;
-      __nv_bfloat16* out_b = p.out + (static_cast<size_t>(head) * p.seq_len + (live_b ? dst_b : 0)) * HD;
+      __nv_bfloat16* out_a = p.out + head * p.out_head_stride + (live_a ? dst_a : 0) * p.out_token_stride;
+      __nv_bfloat16* out_b = p.out + head * p.out_head_stride + (live_b ? dst_b : 0) * p.out_token_stride;
 #pragma unroll
       for (int h = 0; h < HD / 64; ++h) {
         uint32_t o[32];
@@ -572,10 +574,10 @@ int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& 
 static float* g_debug_buffer = nullptr;
 extern "C" void dfs_debug_set_dump(float* device_buffer) { g_debug_buffer = device_buffer; }
 
-extern "C" int dfs_block_sparse_fwd(const void* q, const void* k, const void* v, const int32_t* idx,
-                                    const int32_t* cnt, int kmax, const int32_t* out_row_map, void* out,
-                                    int heads, int64_t seq_len, int64_t kv_len, int head_dim, float scale,
-                                    int32_t* status, void* stream_) {
+extern "C" int dfs_block_sparse_fwd_ex(const void* q, const void* k, const void* v, const int32_t* idx,
+                                       const int32_t* cnt, int kmax, const int32_t* out_row_map, void* out,
+                                       int out_token_major, int heads, int64_t seq_len, int64_t kv_len,
+                                       int head_dim, float scale, int32_t* status, void* stream_) {
   if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return DFS_ERR_NULL;
   if ((idx == nullptr) != (cnt == nullptr)) return DFS_ERR_NULL;
   if (!dfs_aligned16(q) || !dfs_aligned16(k) || !dfs_aligned16(v) || !dfs_aligned16(out)) return DFS_ERR_ALIGN;
@@ -601,10 +603,21 @@ extern "C" int dfs_block_sparse_fwd(const void* q, const void* k, const void* v,
   p.debug = g_debug_buffer;
   p.seq_len = seq_len;
   p.kv_len = kv_len;
+  // [H, L, D] or, token-major, [L, H*D]
+  p.out_head_stride = out_token_major ? head_dim : seq_len * head_dim;
+  p.out_token_stride = out_token_major ? static_cast<long long>(heads) * head_dim : head_dim;
   p.kmax = kmax;
   p.q_blocks = static_cast<int>((seq_len + kBlockM - 1) / kBlockM);
   p.k_blocks = static_cast<int>((kv_len + kBlockN - 1) / kBlockN);
   p.scale_log2 = scale * 1.4426950408889634f;
   return head_dim == 128 ? launch_fwd<128>(mq, mk, mv, p, heads, stream)
                          : launch_fwd<64>(mq, mk, mv, p, heads, stream);
+}
+
+extern "C" int dfs_block_sparse_fwd(const void* q, const void* k, const void* v, const int32_t* idx,
+                                    const int32_t* cnt, int kmax, const int32_t* out_row_map, void* out,
+                                    int heads, int64_t seq_len, int64_t kv_len, int head_dim, float scale,
+                                    int32_t* status, void* stream) {
+  return dfs_block_sparse_fwd_ex(q, k, v, idx, cnt, kmax, out_row_map, out, 0, heads, seq_len, kv_len, head_dim,
+                                 scale, status, stream);
 }

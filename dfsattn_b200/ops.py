@@ -184,21 +184,78 @@ def select_topk(scores, q_rows: int, n_rank: int, k_select: int, dense_row_start
 
 # ---- attention -----------------------------------------------------------------------
 def block_sparse_fwd(q_perm, k_perm, v_perm, idx, cnt, out_row_map=None, kv_len=None, scale=None,
-                     out=None):
+                     out=None, token_major=False):
     """bf16 block-sparse attention over permuted [H, L, D] tensors; ``idx=None``
-    attends every key block (dense)."""
+    attends every key block (dense).  ``token_major=True`` stores the result as
+    [L, H, D] (the layout the output projection reads) instead of [H, L, D]."""
     _need_cuda(q_perm, k_perm, v_perm)
     for t in (q_perm, k_perm, v_perm):
         if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.shape != q_perm.shape:
             raise ValueError("q, k, v must be contiguous bf16 [H, L, D] tensors of one shape")
     H, L, D = q_perm.shape
+    want = (L, H, D) if token_major else (H, L, D)
     if out is None:
-        out = torch.empty_like(q_perm)
+        out = torch.empty(want, dtype=q_perm.dtype, device=q_perm.device)
+    elif tuple(out.shape) != want or not out.is_contiguous() or out.dtype != torch.bfloat16:
+        raise ValueError(f"out must be a contiguous bf16 tensor of shape {want}")
     kv_len = L if kv_len is None else int(kv_len)
     scale = D ** -0.5 if scale is None else float(scale)
     kmax = 0 if idx is None else idx.shape[-1]
-    check(lib.dfs_block_sparse_fwd(q_perm.data_ptr(), k_perm.data_ptr(), v_perm.data_ptr(), _ptr(idx),
-                                   _ptr(cnt), kmax, _ptr(out_row_map), out.data_ptr(), H, L, kv_len, D,
-                                   scale, status_tensor(q_perm.device).data_ptr(),
-                                   _stream(q_perm.device)), "dfs_block_sparse_fwd")
+    check(lib.dfs_block_sparse_fwd_ex(q_perm.data_ptr(), k_perm.data_ptr(), v_perm.data_ptr(), _ptr(idx),
+                                      _ptr(cnt), kmax, _ptr(out_row_map), out.data_ptr(), int(token_major),
+                                      H, L, kv_len, D, scale, status_tensor(q_perm.device).data_ptr(),
+                                      _stream(q_perm.device)), "dfs_block_sparse_fwd_ex")
+    return out
+
+
+# ---- fused pre-attention step ----------------------------------------------------------
+def qkv_prepare(q_src, k_src, v_src, heads: int, *, gamma_q=None, gamma_k=None, eps_q=1e-6, eps_k=1e-6,
+                norm_across_heads=False, cos=None, sin=None, rope_rows=None, perm=None,
+                out=None, out_row0=0, out_len=None):
+    """Projections [rows, H*D] (bf16, token-major) -> (q, k, v) head-major [H, out_len, D], with the
+    RMSNorm, the rotary embedding of the first ``rope_rows`` source rows and the token gather
+    ``perm`` applied on the way (``dfs_qkv_prepare`` in include/dfs_b200.h).  ``out`` is an
+    optional (q, k, v) triple of [H, out_len, D] tensors to fill rows [out_row0, out_row0 + n)."""
+    srcs = (q_src, k_src, v_src)
+    first = next(t for t in srcs if t is not None)
+    _need_cuda(first)
+    for t in srcs:
+        if t is not None and (t.dtype != torch.bfloat16 or not t.is_contiguous() or t.shape != first.shape
+                              or t.dim() != 2):
+            raise ValueError("projections must be contiguous bf16 [rows, H*D] tensors of one shape")
+    rows, hd = first.shape
+    if hd % heads:
+        raise ValueError("row width is not a multiple of the head count")
+    D = hd // heads
+    n = rows if perm is None else perm.numel()
+    out_len = out_row0 + n if out_len is None else int(out_len)
+    if out is None:
+        out = tuple(torch.empty((heads, out_len, D), dtype=torch.bfloat16, device=first.device)
+                    if t is not None else None for t in srcs)
+    for t, o in zip(srcs, out):
+        if (t is None) != (o is None):
+            raise ValueError("out must match the given projections")
+        if o is not None and (tuple(o.shape) != (heads, out_len, D) or not o.is_contiguous()
+                              or o.dtype != torch.bfloat16):
+            raise ValueError(f"outputs must be contiguous bf16 {(heads, out_len, D)}")
+    for g in (gamma_q, gamma_k):
+        if g is not None and (g.dtype != torch.bfloat16 or not g.is_contiguous()
+                              or g.numel() != (hd if norm_across_heads else D)):
+            raise ValueError("norm weights must be contiguous bf16 of D (per head) or H*D elements")
+    rope_dim = 0
+    if cos is not None:
+        if sin is None or cos.shape != sin.shape or cos.dtype != torch.float32 or sin.dtype != torch.float32 \
+                or not (cos.is_contiguous() and sin.is_contiguous()) or cos.dim() != 2:
+            raise ValueError("cos/sin must be contiguous fp32 [rows, D] or [rows, D/2] tables of one shape")
+        rope_dim = cos.shape[1]
+        rope_rows = cos.shape[0] if rope_rows is None else int(rope_rows)
+        if rope_rows > cos.shape[0]:
+            raise ValueError("rope_rows exceeds the table")
+    if perm is not None and (perm.dtype != torch.int32 or not perm.is_contiguous()):
+        raise ValueError("perm must be contiguous int32")
+    check(lib.dfs_qkv_prepare(_ptr(q_src), _ptr(k_src), _ptr(v_src), _ptr(gamma_q), _ptr(gamma_k),
+                              float(eps_q), float(eps_k), int(norm_across_heads), _ptr(cos), _ptr(sin),
+                              rope_dim, int(rope_rows or 0), _ptr(perm), _ptr(out[0]), _ptr(out[1]),
+                              _ptr(out[2]), heads, n, int(out_row0), out_len, D, _stream(first.device)),
+          "dfs_qkv_prepare")
     return out

@@ -91,6 +91,34 @@ int dfs_permute_qkv(const void* q, const void* k, const void* v, const int32_t* 
 int dfs_unpermute(const void* src, const int32_t* inv_perm, void* dst, int heads,
                   int64_t seq_len, int row_bytes, void* stream);
 
+/* ---- fused pre-attention step (processor side) --------------------------- */
+
+/* Token-major projections [rows, H*D] (bf16) -> head-major, normalised, rotated and
+ * token-permuted [H, out_len, D] in one pass:
+ *   out[h, out_row0 + i, :] = rope(rmsnorm(src[row(i), h*D:(h+1)*D])),  row(i) = perm ? perm[i] : i.
+ * Replaces, for Q and K, unflatten/transpose/contiguous (dfsattn/replace_hyvideo.py:247-249,
+ * replace_wan.py:174-176), the RMSNorm (per head: kernels/include/norm/narrow_rms_norm.cuh:22-71 as
+ * called from kernels/__init__.py:34-52; over the whole H*D row: kernels/triton/rmsnorm.py:8-49 as
+ * called at replace_wan.py:162-166), the rotary embedding of the leading rope_rows tokens
+ * (kernels/include/rope/rope_enc.cuh:17-36 and rope_enc_txtlast.cuh:33-75; complex form:
+ * replace_wan.py:207-215) and the Hilbert gather of dfsattn/attention_hyvideo.py:1034-1036; V is
+ * transposed and gathered only.  Arithmetic as in those kernels: fp32, y = (x*rsqrt(mean(x^2)+eps))*gamma
+ * rounded to bf16, then out[i] = y[i]*cos[i] + (i even ? -y[i+1] : y[i-1])*sin[i] rounded to bf16.
+ *  q_src/k_src/v_src : bf16 [src_rows, H*D]; any may be NULL together with its output.
+ *  gamma_q/gamma_k   : bf16 [D] (norm_across_heads == 0) or [H*D] (!= 0); NULL = no norm.
+ *  cos_tab/sin_tab   : fp32 [rope_rows, rope_dim], rope_dim == D (one value per element, pairs hold the
+ *                      same value twice) or D/2 (one value per pair: real and imaginary part of the
+ *                      complex frequencies); NULL = no rotation.  Source rows >= rope_rows (text) are
+ *                      not rotated.
+ *  perm              : int32 [n_rows] or NULL (identity).
+ *  Two calls assemble a tensor whose text rows come from separate projections
+ *  (replace_hyvideo.py:292-312): video rows with out_row0 = 0, text rows with out_row0 = video_len. */
+int dfs_qkv_prepare(const void* q_src, const void* k_src, const void* v_src, const void* gamma_q,
+                    const void* gamma_k, float eps_q, float eps_k, int norm_across_heads,
+                    const float* cos_tab, const float* sin_tab, int rope_dim, int64_t rope_rows,
+                    const int32_t* perm, void* q_out, void* k_out, void* v_out, int heads,
+                    int64_t n_rows, int64_t out_row0, int64_t out_len, int head_dim, void* stream);
+
 /* ---- scoring + selection ------------------------------------------------ */
 
 /* Bytes of scratch dfs_block_scores needs for this shape. */
@@ -173,6 +201,15 @@ int dfs_block_sparse_fwd(const void* q, const void* k, const void* v, const int3
                          const int32_t* cnt, int kmax, const int32_t* out_row_map, void* out,
                          int heads, int64_t seq_len, int64_t kv_len, int head_dim, float scale,
                          int32_t* status, void* stream);
+
+/* dfs_block_sparse_fwd with a choice of output layout: out_token_major == 0 stores [H, L, D] as
+ * above; != 0 stores token-major [L, H*D], which is what the output projection reads, so that the
+ * transpose(1, 2).flatten(2, 3) copy after the attention call (dfsattn/replace_hyvideo.py:443,
+ * replace_wan.py:311) disappears together with the inverse permute. */
+int dfs_block_sparse_fwd_ex(const void* q, const void* k, const void* v, const int32_t* idx,
+                            const int32_t* cnt, int kmax, const int32_t* out_row_map, void* out,
+                            int out_token_major, int heads, int64_t seq_len, int64_t kv_len,
+                            int head_dim, float scale, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }
