@@ -177,9 +177,11 @@ def valid_length(cu_seqlens, seq_len: int) -> int:
     return seq_len if valid <= 0 or valid > seq_len else valid
 
 
-def run_attention(qp, kp, vp, lists: Optional[BlockLists], perm_i32, valid_len: int) -> torch.Tensor:
+def run_attention(qp, kp, vp, lists: Optional[BlockLists], perm_i32, valid_len: int,
+                  token_major: bool = False) -> torch.Tensor:
     """Block-sparse (or dense when ``lists`` is None) attention on permuted
-    bf16 [H,L,D]; returns the un-permuted result [H,L,D].
+    bf16 [H,L,D]; returns the un-permuted result, [H,L,D] or, with
+    ``token_major``, [L,H,D] (what the output projection reads).
 
     A padded tail [valid_len, L) forms a second, independent varlen segment
     whose block coordinates restart at zero (block_sparse_attn semantics,
@@ -189,7 +191,8 @@ def run_attention(qp, kp, vp, lists: Optional[BlockLists], perm_i32, valid_len: 
     H, L, D = qp.shape
     idx = lists.idx if lists is not None else None
     cnt = lists.cnt if lists is not None else None
-    out = ops.block_sparse_fwd(qp, kp, vp, idx, cnt, out_row_map=perm_i32, kv_len=valid_len)
+    out = ops.block_sparse_fwd(qp, kp, vp, idx, cnt, out_row_map=perm_i32, kv_len=valid_len,
+                               token_major=token_major)
     if valid_len < L:
         tail = L - valid_len
         if perm_i32 is not None and not bool((perm_i32[valid_len:] == torch.arange(
@@ -202,5 +205,15 @@ def run_attention(qp, kp, vp, lists: Optional[BlockLists], perm_i32, valid_len: 
             lists2 = BlockLists.from_bool_mask(lists.to_bool_mask()[:, :nb2, :nb2].contiguous())
         o2 = ops.block_sparse_fwd(q2, k2, v2, None if lists2 is None else lists2.idx,
                                   None if lists2 is None else lists2.cnt, kv_len=tail)
-        out[:, valid_len:] = o2
+        if token_major:
+            out[valid_len:] = o2.permute(1, 0, 2)
+        else:
+            out[:, valid_len:] = o2
     return out
+
+
+def as_reference_layout(out: torch.Tensor, token_major: bool) -> torch.Tensor:
+    """[H,L,D] or token-major [L,H,D] -> the operator's result shape [1,H,L,D].  For a
+    token-major buffer this is a view whose ``transpose(1, 2).flatten(2, 3)`` (what the
+    processors do next) is again a view: no copy between attention and output projection."""
+    return (out.permute(1, 0, 2) if token_major else out).unsqueeze(0)

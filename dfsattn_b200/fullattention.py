@@ -11,8 +11,14 @@ from . import engine, ops
 
 
 def full_attention(q, k, v, mode="flash", drop_rate=0, attn_mask=None, causal=False, cu_seqlens_q=None,
-                   cu_seqlens_kv=None, max_seqlen_q=None, max_seqlen_kv=None, batch_size=1):
-    """q, k, v: [1, H, L, D] -> [1, H, L, D] (same layout as the sparse operator)."""
+                   cu_seqlens_kv=None, max_seqlen_q=None, max_seqlen_kv=None, batch_size=1, out_row_map=None,
+                   token_major_out=False):
+    """q, k, v: [1, H, L, D] -> [1, H, L, D] (same layout as the sparse operator).
+
+    Two additions for the fused processor path: ``out_row_map`` (int32 [L]) stores the result of
+    query row i at row out_row_map[i] -- dense attention does not care about the key order, so
+    inputs that were written in a permuted token order only need their rows put back -- and
+    ``token_major_out`` keeps the result as [L, H, D] memory behind the [1, H, L, D] shape."""
     if mode != "flash":
         raise ValueError(f"full_attention mode={mode!r}: only 'flash' (dense varlen) is built for B200")
     if causal or drop_rate:
@@ -21,5 +27,5 @@ def full_attention(q, k, v, mode="flash", drop_rate=0, attn_mask=None, causal=Fa
     L = q.shape[2]
     qh, kh, vh = engine.prepare_inputs(q, k, v)
     valid = engine.valid_length(cu_seqlens_kv if cu_seqlens_kv is not None else cu_seqlens_q, L)
-    out = engine.run_attention(qh, kh, vh, None, None, valid)
-    return out.unsqueeze(0).to(out_dtype)
+    out = engine.run_attention(qh, kh, vh, None, out_row_map, valid, token_major=token_major_out)
+    return engine.as_reference_layout(out, token_major_out).to(out_dtype)

@@ -12,6 +12,7 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
+from . import fused_qkv
 from .attention_hyvideo import DFS_Attention, dfs_attention
 from .fullattention import full_attention
 
@@ -87,11 +88,55 @@ class HunyuanVideo_DFSAttn_Processor2_0:
                           and (self.step_idx - self.skip_steps + 1) % self.dense_interval == 0)
         return self.layer_idx not in self.skip_layers and in_sparse and not periodic_dense
 
+    # One pass from the projections to permuted, normalised, rotated Q/K/V and a token-major
+    # attention result (no transpose before the output projection).  Class-wide switch; calls the
+    # fused kernel does not cover take the unfused path below.
+    fused_prepare = True
+
+    def _fused_qkv(self, attn, hidden_states, encoder_hidden_states, image_rotary_emb, single_stream):
+        """(q, k, v [1,H,L,D] in permuted token order, perm) or None when the call is not eligible."""
+        width = attn.to_q.out_features if hasattr(attn.to_q, "out_features") else None
+        if width is None or not fused_qkv.eligible(hidden_states, attn.heads, width):
+            return None
+        heads = attn.heads
+        double_stream = getattr(attn, "add_q_proj", None) is not None and encoder_hidden_states is not None
+        n_main = hidden_states.shape[1]
+        n_text = encoder_hidden_states.shape[1] if double_stream else 0
+        seq_len = n_main + n_text
+        text_in_main = encoder_hidden_states.shape[1] if single_stream else 0
+        video_len = n_main - text_in_main                                 # rows that get the rotation
+        perm_video_len = self.video_len if self.video_len else seq_len    # as the operator builds its permutation
+        if perm_video_len > seq_len or (double_stream and perm_video_len > n_main):
+            return None
+        try:
+            perm = fused_qkv.token_perm(self.video_perm, seq_len, perm_video_len, hidden_states.device) \
+                if self.video_perm is not None else None
+            main_perm = perm[:n_main] if (perm is not None and double_stream) else perm
+            out = fused_qkv.prepare(attn.to_q(hidden_states), attn.to_k(hidden_states), attn.to_v(hidden_states),
+                                    heads, getattr(attn, "norm_q", None), getattr(attn, "norm_k", None),
+                                    image_rotary_emb, video_len, main_perm, out_row0=0, out_len=seq_len)
+            if double_stream:
+                fused_qkv.prepare(attn.add_q_proj(encoder_hidden_states), attn.add_k_proj(encoder_hidden_states),
+                                  attn.add_v_proj(encoder_hidden_states), heads,
+                                  getattr(attn, "norm_added_q", None), getattr(attn, "norm_added_k", None),
+                                  None, 0, None, out=out, out_row0=n_main, out_len=seq_len)
+        except TypeError:
+            return None
+        return tuple(t.unsqueeze(0) for t in out), perm
+
     def __call__(self, attn, hidden_states: torch.Tensor, encoder_hidden_states: Optional[torch.Tensor] = None,
                  attention_mask: Optional[torch.Tensor] = None, image_rotary_emb=None):
         single_stream = getattr(attn, "add_q_proj", None) is None and encoder_hidden_states is not None
         if single_stream:
             hidden_states = torch.cat([hidden_states, encoder_hidden_states], dim=1)
+
+        fused = self._fused_qkv(attn, hidden_states, encoder_hidden_states, image_rotary_emb, single_stream) \
+            if self.fused_prepare else None
+        self.last_call_fused = fused is not None   # for tests and logs: which path this call took
+        if fused is not None:
+            (query, key, value), perm = fused
+            return self._attend_and_project(attn, query, key, value, encoder_hidden_states, attention_mask,
+                                            prepermuted=True, perm=perm)
 
         query = attn.to_q(hidden_states).unflatten(2, (attn.heads, -1)).transpose(1, 2).contiguous()
         key = attn.to_k(hidden_states).unflatten(2, (attn.heads, -1)).transpose(1, 2).contiguous()
@@ -121,7 +166,13 @@ class HunyuanVideo_DFSAttn_Processor2_0:
             query = torch.cat([query, eq], dim=2)
             key = torch.cat([key, ek], dim=2)
             value = torch.cat([value, ev], dim=2)
+        return self._attend_and_project(attn, query, key, value, encoder_hidden_states, attention_mask)
 
+    def _attend_and_project(self, attn, query, key, value, encoder_hidden_states, attention_mask,
+                            prepermuted: bool = False, perm=None):
+        """Steps 5 and 6 of the reference processor (replace_hyvideo.py:314-464).  With
+        ``prepermuted`` the inputs are in the permuted token order and the result comes back
+        token-major, so the transpose below is a view."""
         if attention_mask is not None:
             cu_q, cu_kv, max_q, max_kv = self.get_cu_max_seqlen(attention_mask, query.device)
         else:
@@ -139,12 +190,15 @@ class HunyuanVideo_DFSAttn_Processor2_0:
                 max_seqlen_q=max_q, max_seqlen_kv=max_kv, sparse_execution=self.sparse_execution,
                 hybrid_threshold=self.hybrid_threshold, block_top_p=self.block_top_p,
                 token_top_k=self.token_top_k, residual_candidate_blocks=self.residual_candidate_blocks,
-                selector_mode=self.selector_mode, fine_top_p=self.fine_top_p)
+                selector_mode=self.selector_mode, fine_top_p=self.fine_top_p, prepermuted=prepermuted,
+                token_major_out=prepermuted)
         else:
             t0 = rec.start(query.device)
             hidden_states = full_attention(query, key, value, mode="flash", drop_rate=0.0, attn_mask=None,
                                            causal=False, cu_seqlens_q=cu_q, cu_seqlens_kv=cu_kv,
-                                           max_seqlen_q=max_q, max_seqlen_kv=max_kv, batch_size=query.shape[0])
+                                           max_seqlen_q=max_q, max_seqlen_kv=max_kv, batch_size=query.shape[0],
+                                           out_row_map=perm if prepermuted else None,
+                                           token_major_out=prepermuted)
             rec.stop(t0, phase="attention_execution", step_idx=self.step_idx, layer_idx=self.layer_idx,
                      device=query.device)
 

@@ -12,6 +12,7 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
+from . import fused_qkv
 from .attention_wan import DFS_Attention, dfs_attention
 from .fullattention import full_attention
 
@@ -75,6 +76,43 @@ class Wan_DFSAttn_Processor2_0:
             return "sparse"
         return "dense"
 
+    # One pass from the projections to permuted, normalised, rotated Q/K/V and a token-major
+    # attention result; class-wide switch, self-attention only (cross-attention is not on the path).
+    fused_prepare = True
+
+    def _fused_self_attention(self, attn, hidden_states, rotary_emb):
+        width = getattr(attn.to_q, "out_features", None)
+        if width is None or not fused_qkv.eligible(hidden_states, attn.heads, width):
+            return None
+        S = hidden_states.shape[1]
+        try:
+            perm = fused_qkv.token_perm(self.video_perm, S, S, hidden_states.device) \
+                if self.video_perm is not None else None
+            out = fused_qkv.prepare(attn.to_q(hidden_states), attn.to_k(hidden_states), attn.to_v(hidden_states),
+                                    attn.heads, getattr(attn, "norm_q", None), getattr(attn, "norm_k", None),
+                                    rotary_emb, S, perm)
+        except TypeError:
+            return None
+        query, key, value = (t.unsqueeze(0) for t in out)
+        if self._gate() == "sparse":
+            hidden_states = dfs_attention(
+                query, key, value, step_idx=self.step_idx, skip_steps=self.skip_steps,
+                cache_interval=self.cache_interval, layer_idx=self.layer_idx, sparsity=self.sparsity,
+                sparsity_dcrt=self.sparsity_dcrt, tile_size=self.tile_size, block_size=self.block_size,
+                video_perm=self.video_perm, cache_flag=self.cache_flag, record_density=self.record_density,
+                max_seqlen_q=S, max_seqlen_kv=S, sparse_execution=self.sparse_execution,
+                hybrid_threshold=self.hybrid_threshold, prepermuted=True, token_major_out=True)
+        else:
+            hidden_states = full_attention(query, key, value, mode="flash", max_seqlen_q=S, max_seqlen_kv=S,
+                                           batch_size=1, out_row_map=perm, token_major_out=True)
+        hidden_states = hidden_states.transpose(1, 2).flatten(2, 3).type_as(query)  # a view
+        hidden_states = attn.to_out[0](hidden_states)
+        hidden_states = attn.to_out[1](hidden_states)
+        self.step_idx += 1
+        if self.step_idx == self.num_inference_steps * 2:
+            self.step_idx = 0
+        return hidden_states
+
     def __call__(self, attn, hidden_states: torch.Tensor, encoder_hidden_states: Optional[torch.Tensor] = None,
                  attention_mask: Optional[torch.Tensor] = None, rotary_emb: Optional[torch.Tensor] = None):
         encoder_hidden_states_img = None
@@ -82,8 +120,16 @@ class Wan_DFSAttn_Processor2_0:
             image_context_length = encoder_hidden_states.shape[1] - 512
             encoder_hidden_states_img = encoder_hidden_states[:, :image_context_length]
             encoder_hidden_states = encoder_hidden_states[:, image_context_length:]
+        self_attention = encoder_hidden_states is None
         if encoder_hidden_states is None:
             encoder_hidden_states = hidden_states
+
+        self.last_call_fused = False   # for tests and logs: which path this call took
+        if self.fused_prepare and self_attention and attention_mask is None:
+            fused = self._fused_self_attention(attn, hidden_states, rotary_emb)
+            if fused is not None:
+                self.last_call_fused = True
+                return fused
 
         query = attn.to_q(hidden_states)
         key = attn.to_k(encoder_hidden_states)

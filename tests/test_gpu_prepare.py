@@ -118,3 +118,92 @@ def test_token_major_output_equals_the_transposed_head_major_output(ops, L, H, D
     b = ops.block_sparse_fwd(q, k, v, idx.cuda(), cnt.cuda(), out_row_map=rowmap, token_major=True)
     assert b.shape == (L, H, D)
     assert torch.equal(a.permute(1, 0, 2).contiguous(), b)
+
+
+# ---- the processors' fused path against their unfused (reference-shaped) path -------------------
+class _Attn(torch.nn.Module):
+    """Duck-typed stand-in for a diffusers Attention block with RMSNorms."""
+
+    def __init__(self, dim, heads, norm_width, added=False):
+        super().__init__()
+        self.heads = heads
+        self.to_q, self.to_k, self.to_v = (torch.nn.Linear(dim, dim) for _ in range(3))
+        self.norm_q, self.norm_k = (torch.nn.RMSNorm(norm_width, eps=1e-6) for _ in range(2))
+        self.to_out = torch.nn.ModuleList([torch.nn.Linear(dim, dim), torch.nn.Identity()])
+        self.add_q_proj = self.add_k_proj = self.add_v_proj = None
+        self.norm_added_q = self.norm_added_k = None
+        self.to_add_out = None
+        if added:
+            self.add_q_proj, self.add_k_proj, self.add_v_proj = (torch.nn.Linear(dim, dim) for _ in range(3))
+            self.norm_added_q, self.norm_added_k = (torch.nn.RMSNorm(norm_width, eps=1e-6) for _ in range(2))
+            self.to_add_out = torch.nn.Linear(dim, dim)
+        with torch.no_grad():
+            for m in self.modules():
+                if isinstance(m, torch.nn.RMSNorm):
+                    m.weight.uniform_(0.5, 1.5)
+
+
+def _reset_operator_state():
+    from dfsattn_b200 import attention_hyvideo as hy, attention_wan as wan
+    for m in (hy, wan):
+        m.DFS_Attention.clear_cache()
+        m._dfs_attention_instances.clear()
+
+
+def _close(a, b, cos_min=0.9995, max_abs=6e-2):
+    import oracle
+    m = oracle.tensor_metrics(a.detach().float().cpu(), b.detach().float().cpu())
+    assert m["cosine"] >= cos_min and m["max_abs"] <= max_abs, m
+
+
+@pytest.mark.parametrize("added", [False, True])
+def test_hyvideo_processor_fused_path_matches_unfused(ops, added):
+    from dfsattn_b200.replace_hyvideo import HunyuanVideo_DFSAttn_Processor2_0 as P
+    from dfsattn_b200.order import hilbert3d_perm
+    torch.manual_seed(1)
+    _reset_operator_state()
+    grid, text, heads, D = (3, 8, 16), 64, 2, 128
+    V = grid[0] * grid[1] * grid[2]
+    attn = _Attn(heads * D, heads, D, added=added).cuda().bfloat16()
+    hs = torch.randn(1, V, heads * D, device="cuda", dtype=torch.bfloat16)
+    enc = torch.randn(1, text, heads * D, device="cuda", dtype=torch.bfloat16)
+    am = torch.ones(1, V + text, dtype=torch.bool, device="cuda")
+    ang = torch.rand(V, D // 2, device="cuda") * 6.28
+    rope = (ang.cos().repeat_interleave(2, 1), ang.sin().repeat_interleave(2, 1))
+    args = ("dfs", 0.5, 16, 128, V, hilbert3d_perm(*grid), 3, [], 1, 4, 0.0, True)
+    slow, fast = P(*args), P(*args)
+    slow.fused_prepare = False
+    for step in range(3):   # step 0 dense, step 1 refresh (slow fills the cache, fast reuses it), step 2 cached
+        slow.step_idx = fast.step_idx = step
+        o1, e1 = slow(attn, hs, enc, attention_mask=am, image_rotary_emb=rope)
+        if step == 1:
+            fast.step_idx = 2   # same layer, no refresh: the lists the unfused call just stored
+        o2, e2 = fast(attn, hs, enc, attention_mask=am, image_rotary_emb=rope)
+        assert fast.last_call_fused and not slow.last_call_fused
+        assert o2.shape == o1.shape and e2.shape == e1.shape
+        _close(o2, o1)
+        _close(e2, e1)
+
+
+def test_wan_processor_fused_path_matches_unfused(ops):
+    from dfsattn_b200.replace_wan import Wan_DFSAttn_Processor2_0 as P
+    from dfsattn_b200.order import hilbert3d_perm
+    torch.manual_seed(2)
+    _reset_operator_state()
+    grid, heads, D = (2, 8, 16), 2, 128
+    V = grid[0] * grid[1] * grid[2]
+    attn = _Attn(heads * D, heads, heads * D).cuda().bfloat16()
+    hs = torch.randn(1, V, heads * D, device="cuda", dtype=torch.bfloat16)
+    ang = torch.rand(V, D // 2, device="cuda", dtype=torch.float64) * 6.28
+    freqs = torch.polar(torch.ones_like(ang), ang)[None, None]
+    args = ("dfs", 0.5, 16, 128, hilbert3d_perm(*grid), 1, [], 1, 4, 0.0, True, False)
+    slow, fast = P(*args), P(*args)
+    slow.fused_prepare = False
+    for step in (0, 2, 3):   # dense; refresh by the unfused call; the fused call reuses its lists
+        slow.step_idx = fast.step_idx = step
+        o1 = slow(attn, hs, rotary_emb=freqs)
+        if step == 2:
+            fast.step_idx = 3
+        o2 = fast(attn, hs, rotary_emb=freqs)
+        assert fast.last_call_fused and not slow.last_call_fused
+        _close(o2, o1)
