@@ -307,6 +307,20 @@ def run_gpu(args, spec, rank, local_rank, world):
         "attention_ms": 1e3 * t_attn,
     }
 
+    # The processor-side fused step that makes the permute above unnecessary: projections
+    # [L, H*D] -> normalised, rotated, permuted head-major Q/K/V in one pass (not part of `value`).
+    src = [torch.randn(L, h_local * D, device=dev, dtype=torch.bfloat16) for _ in range(3)]
+    gam = torch.ones(D if hy else h_local * D, device=dev, dtype=torch.bfloat16)
+    ang = torch.rand(video_len, D // 2, device=dev) * 6.2831853
+    tabs = (ang.cos().repeat_interleave(2, 1).contiguous(), ang.sin().repeat_interleave(2, 1).contiguous()) \
+        if hy else (ang.cos(), ang.sin())
+    prep = lambda: ops.qkv_prepare(*src, h_local, gamma_q=gam, gamma_k=gam, norm_across_heads=not hy,  # noqa: E731
+                                   cos=tabs[0], sin=tabs[1], rope_rows=video_len, perm=perm, out=(qp, kp, vp))
+    t_prep = timed(prep, n_stage, barrier, warm=2) / n_stage
+    stages["fused_prepare_ms"] = 1e3 * t_prep
+    stages["fused_prepare_gbs"] = 6 * tensor_bytes / t_prep / 1e9
+    del src, ang, tabs
+
     # ---- end to end through the public API with HOST buffers ----------------
     hq, hk, hv = (t.cpu().pin_memory() for t in step_inputs)
     hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
