@@ -341,7 +341,7 @@ def run_gpu(args, spec, rank, local_rank, world):
             dv.copy_(hv, non_blocking=True)
             hout.copy_(call(dq, dk, dv), non_blocking=True)
         else:           # the host-buffer entry point: copies of head groups overlap the kernels
-            dfs_attention_host(hq, hk, hv, out=hout, head_groups=4, device=dev,
+            dfs_attention_host(hq, hk, hv, out=hout, head_groups=args.e2e_head_groups, device=dev,
                                flavor="hyvideo" if hy else "wan", layer_idx=1000, **host_kw)
 
     n_e2e = max(2, min(args.steps, 5))
@@ -404,6 +404,8 @@ def main():
     ap.add_argument("--sparsity", type=float, default=None, help="override the workload's sparsity")
     ap.add_argument("--order", default="hilbert3d", choices=["hilbert3d", "org"],
                     help="token order: 3-D Hilbert curve or raster (no permutation)")
+    ap.add_argument("--e2e-head-groups", type=int, default=12,
+                    help="head groups the host-buffer entry point pipelines its copies over")
     ap.add_argument("--layout", default="head", choices=["head", "seq"],
                     help="how inputs arrive at N > 1: head shards (no collective) or sequence shards")
     args = ap.parse_args()
