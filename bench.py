@@ -17,7 +17,6 @@ counted exactly) / step time; ms_per_step is the time per call.
 """
 import argparse
 import json
-import math
 import os
 import subprocess
 import sys

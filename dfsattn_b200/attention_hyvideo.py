@@ -9,7 +9,6 @@ calls into libdfs_b200.so; masks are kept as device-resident index lists.
 Knobs of the reference's other backends are accepted and rejected with
 ``ValueError`` -- there is no dispatch and no fallback.
 """
-import math
 import os
 from typing import Any, Dict, Optional, Tuple
 

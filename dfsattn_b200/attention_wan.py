@@ -16,7 +16,6 @@ import torch
 
 from . import attention_hyvideo as _hy
 from .attention_hyvideo import _compute_cache_schedule  # noqa: F401  (same schedule function)
-from .timing import AttentionTimingRecorder
 
 _dfs_attention_instances: Dict[int, "DFS_Attention"] = {}
 

@@ -5,9 +5,7 @@ the processors use (``"flash"``: varlen attention with cu_seqlens = [0, valid,
 L]).  It is the block-sparse kernel with every key block listed -- one
 back-end, no flash-attn dependency.
 """
-import torch
-
-from . import engine, ops
+from . import engine
 
 
 def full_attention(q, k, v, mode="flash", drop_rate=0, attn_mask=None, causal=False, cu_seqlens_q=None,

@@ -8,7 +8,6 @@ from typing import Optional, Tuple
 
 import torch
 
-from . import _lib
 from ._lib import check, lib
 
 BLOCK = 128

@@ -13,7 +13,7 @@ the sequence; the output goes back through one all-to-all.  The collective is
 CPU tests); everything a kernel reads has landed in local memory before the
 kernel runs.
 """
-from typing import List, Optional, Tuple
+from typing import List, Tuple
 
 import torch
 import torch.distributed as dist

@@ -10,7 +10,6 @@ same projections); diffusers itself is not imported.
 from typing import Optional
 
 import torch
-import torch.nn.functional as F
 
 from . import fused_qkv
 from .attention_hyvideo import DFS_Attention, dfs_attention

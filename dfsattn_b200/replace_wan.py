@@ -13,7 +13,7 @@ import torch
 import torch.nn.functional as F
 
 from . import fused_qkv
-from .attention_wan import DFS_Attention, dfs_attention
+from .attention_wan import dfs_attention
 from .fullattention import full_attention
 
 

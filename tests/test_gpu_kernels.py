@@ -2,7 +2,6 @@
 through the C ABI (dfsattn_b200.ops wraps one entry point per function)."""
 import math
 
-import numpy as np
 import pytest
 import torch
 

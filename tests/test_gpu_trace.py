@@ -21,7 +21,6 @@ def _close(got, want):
 def test_hunyuan_trace_small():
     if not torch.cuda.is_available():
         pytest.skip("needs a GPU")
-    from dfsattn_b200.replace_hyvideo import HunyuanVideo_DFSAttn_Processor2_0
     from dfsattn_b200.attention_hyvideo import DFS_Attention, _dfs_attention_instances, dfs_attention
     from dfsattn_b200.fullattention import full_attention
     from dfsattn_b200.order import hilbert3d_perm
