@@ -36,6 +36,11 @@ WORKLOADS = {
     "wan_480p_h8": dict(grid=(21, 30, 52), text=0, heads=8, dim=128, sparsity=0.3, flavor="wan"),
     "hunyuan_480p_h4": dict(grid=(33, 30, 45), text=256, heads=4, dim=128, sparsity=0.3, flavor="hyvideo"),
     "tiny": dict(grid=(4, 16, 16), text=0, heads=2, dim=64, sparsity=0.3, flavor="hyvideo"),
+    # the mask-caching trace: 50 denoising steps (12 dense, refreshes at 12 / 24 / 36 with sparsity
+    # 0.3 / 0.2 / 0.1) over --trace-layers layers with drifting Q/K; one bench step = the whole trace
+    "hunyuan_720p_trace": dict(grid=(33, 45, 80), text=256, heads=24, dim=128, sparsity=0.3, flavor="hyvideo",
+                               trace=True),
+    "tiny_trace": dict(grid=(4, 16, 16), text=64, heads=2, dim=128, sparsity=0.5, flavor="hyvideo", trace=True),
 }
 METRIC = "dfs_attn_effective_tflops"
 UNIT = "TFLOP/s"
@@ -189,6 +194,132 @@ def timed(fn, steps, barrier, warm=0):
     torch.cuda.synchronize()
     barrier()
     return e0.elapsed_time(e1) / 1e3  # seconds
+
+
+def run_trace(args, spec, rank, local_rank, world):
+    """The mask-caching trace on the GPU: per denoising step and layer either the dense call (warm-up
+    steps), a refresh call (score + select + attention) or a call on cached lists, Q and K drifting
+    from step to step (x <- 0.98 x + 0.2 N(0,1), outside the timed intervals).  One bench step is the
+    whole 50-step trace; the time is the sum of the CUDA-event intervals around the attention calls."""
+    import torch.distributed as dist
+    from dfsattn_b200 import ops
+    from dfsattn_b200.attention_hyvideo import (DFS_Attention, _compute_cache_schedule, _dfs_attention_instances,
+                                                dfs_attention)
+    from dfsattn_b200.fullattention import full_attention
+    from dfsattn_b200.order import hilbert3d_perm
+    from dfsattn_b200.synthetic import drift, structured_qkv
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    H, D = spec["heads"], spec["dim"]
+    if H % world != 0:
+        raise SystemExit(f"{H} heads do not split over {world} ranks")
+    h_local = H // world
+    layers, n_steps, skip, interval, s0, dcrt = args.trace_layers, 50, 12, 12, spec["sparsity"], 0.1
+    vperm = hilbert3d_perm(*spec["grid"])
+    base = [structured_qkv(spec["grid"], h_local, D, text_len=spec["text"], dtype=torch.bfloat16, device=dev,
+                           seed=layer, head_offset=rank * h_local, total_heads=H) for layer in range(layers)]
+    L = base[0][0].shape[2]
+    video_len = L - spec["text"]
+
+    def one_trace():
+        DFS_Attention.clear_cache()
+        _dfs_attention_instances.clear()
+        state = [list(t) for t in base]
+        spans = []   # (kind, sparsity, start event, end event)
+        for step in range(n_steps):
+            flag, cur = _compute_cache_schedule(step, skip, interval, s0, dcrt)
+            for layer in range(layers):
+                q, k, v = state[layer]
+                if step > 0:
+                    q = drift(q, 1000 * layer + step)
+                    k = drift(k, 500000 + 1000 * layer + step)
+                    state[layer][0], state[layer][1] = q, k
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                if step < skip:
+                    full_attention(q, k, v, mode="flash")
+                    kind = "dense"
+                else:
+                    dfs_attention(q, k, v, step_idx=step, skip_steps=skip, cache_interval=interval, layer_idx=layer,
+                                  sparsity=s0, sparsity_dcrt=dcrt, tile_size=16, block_size=128,
+                                  video_len=video_len, video_perm=vperm)
+                    kind = "refresh" if flag else "cached"
+                e1.record()
+                spans.append((kind, round(cur, 6), e0, e1))
+        torch.cuda.synchronize()
+        return spans
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    for _ in range(args.warmup):
+        one_trace()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    totals, per_kind = [], {}
+    for _ in range(args.steps):
+        spans = one_trace()
+        ms = [(kind, s, e0.elapsed_time(e1)) for kind, s, e0, e1 in spans]
+        totals.append(sum(t for _, _, t in ms))
+        for kind, s, t in ms:
+            key = kind if kind == "dense" else f"{kind}@{s:g}"
+            per_kind.setdefault(key, []).append(t)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ops.check_status(dev)
+    # algorithmic FLOPs of one trace: dense calls 4*D*L^2 per head, sparse calls 4*D*pairs of their lists
+    pairs = {}
+    for key, entry in DFS_Attention._cached_metadata.items():
+        lists = entry["block_lists"]
+        pairs[(key[0], round(key[4], 6))] = ops.interaction_count(lists.idx, lists.cnt, h_local, L)
+    flops = 0.0
+    for step in range(n_steps):
+        _, cur = _compute_cache_schedule(step, skip, interval, s0, dcrt)
+        for layer in range(layers):
+            flops += 4.0 * D * (h_local * L * L if step < skip else pairs[(layer, round(cur, 6))])
+    secs = sum(totals) / len(totals) / 1e3
+    if world > 1:
+        t = torch.tensor([secs, flops], dtype=torch.float64, device=dev)
+        mx = t.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        secs, flops = float(mx[0]), float(t[1])
+    if rank == 0:
+        pk = peaks()
+        value = flops / secs / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * secs, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "grid": list(spec["grid"]), "text_tokens": spec["text"],
+                       "seq_len": L, "heads": H, "heads_per_gpu": h_local, "head_dim": D, "layers": layers,
+                       "denoising_steps": n_steps, "schedule": {"skip_steps": skip, "cache_interval": interval,
+                                                                "sparsity": s0, "sparsity_dcrt": dcrt},
+                       "step": "one 50-step trace: dense warm-up calls, refresh calls, calls on cached lists",
+                       "parallelism": f"head-sharded x{world}, no collective",
+                       "l2": "inputs larger than L2 (no flush needed)", "flops_per_trace": flops},
+            "clocks": clocks,
+            # dense call: the attention kernel; cached: permute + attention; refresh: + pool, tile LSE,
+            # block sums and selection
+            "gpu_launches": sum(len(v) * (1 if k == "dense" else 6 if k.startswith("refresh") else 2)
+                                for k, v in per_kind.items()),
+            "calls_ms": {k: {"calls_per_trace": len(v) // args.steps, "mean_ms": sum(v) / len(v)}
+                         for k, v in sorted(per_kind.items())},
+            "roofline": {"bound": "tensor", "kernel": "bsattn_fwd_kernel<128>", "achieved": value,
+                         "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                         "frac": value / pk["bf16_tflops_sustained"],
+                         "peak_source": f"{pk['source']} sustained cuBLAS bf16", "traffic": None},
+            "e2e": None, "cpu_baseline": None,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_gpu(args, spec, rank, local_rank, world):
@@ -405,6 +536,7 @@ def main():
                     help="token order: 3-D Hilbert curve or raster (no permutation)")
     ap.add_argument("--e2e-head-groups", type=int, default=12,
                     help="head groups the host-buffer entry point pipelines its copies over")
+    ap.add_argument("--trace-layers", type=int, default=2, help="layers of the *_trace workloads")
     ap.add_argument("--layout", default="head", choices=["head", "seq"],
                     help="how inputs arrive at N > 1: head shards (no collective) or sequence shards")
     args = ap.parse_args()
@@ -418,7 +550,10 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
-    run_gpu(args, spec, rank, local_rank, world)
+    if spec.get("trace"):
+        run_trace(args, spec, rank, local_rank, world)
+    else:
+        run_gpu(args, spec, rank, local_rank, world)
 
 
 if __name__ == "__main__":
