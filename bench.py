@@ -40,7 +40,7 @@ WORKLOADS = {
     # 0.3 / 0.2 / 0.1) over --trace-layers layers with drifting Q/K; one bench step = the whole trace
     "hunyuan_720p_trace": dict(grid=(33, 45, 80), text=256, heads=24, dim=128, sparsity=0.3, flavor="hyvideo",
                                trace=True),
-    "tiny_trace": dict(grid=(4, 16, 16), text=64, heads=2, dim=128, sparsity=0.5, flavor="hyvideo", trace=True),
+    "tiny_trace": dict(grid=(5, 16, 32), text=64, heads=2, dim=128, sparsity=0.5, flavor="hyvideo", trace=True),
 }
 METRIC = "dfs_attn_effective_tflops"
 UNIT = "TFLOP/s"
