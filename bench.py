@@ -179,21 +179,31 @@ def run_reference(args, spec, rank, world):
 # --------------------------------------------------------------------------- #
 # GPU arm
 # --------------------------------------------------------------------------- #
-def timed(fn, steps, barrier, warm=0):
+def timed(fn, steps, barrier, warm=0, per_step=None):
     """CUDA-event time of `steps` calls on the current stream, bracketed by barrier + synchronize;
-    `warm` untimed calls first (they let torch's allocator settle)."""
+    `warm` untimed calls first (they let torch's allocator settle).  With a list in `per_step`, an
+    event after every call also gives each step's own time in ms (appended to the list)."""
     for _ in range(warm):
         fn()
     barrier()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    marks[0].record()
+    for i in range(steps):
         fn()
-    e1.record()
+        if per_step is not None or i == steps - 1:
+            marks[i + 1].record()
     torch.cuda.synchronize()
     barrier()
-    return e0.elapsed_time(e1) / 1e3  # seconds
+    if per_step is not None:
+        per_step.extend(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
+    return marks[0].elapsed_time(marks[steps]) / 1e3  # seconds
+
+
+def quartiles(xs):
+    xs = sorted(xs)
+    at = lambda f: xs[min(len(xs) - 1, max(0, round(f * (len(xs) - 1))))]  # noqa: E731
+    return {"median": at(0.5), "p25": at(0.25), "p75": at(0.75)}
 
 
 def run_trace(args, spec, rank, local_rank, world):
@@ -351,7 +361,8 @@ def run_gpu(args, spec, rank, local_rank, world):
         raise SystemExit(f"{H} heads do not split over {world} ranks")
     h_local = H // world
     f, h, w = spec["grid"]
-    seq_layout = args.layout == "seq" and world > 1
+    seq_layout = args.layout in ("seq", "seq-fused") and world > 1
+    fused_exchange = args.layout == "seq-fused" and world > 1
     if seq_layout:
         # sequence-sharded inputs: every rank holds all heads for its contiguous range of raster tokens
         from dfsattn_b200 import parallel
@@ -372,17 +383,28 @@ def run_gpu(args, spec, rank, local_rank, world):
     hy = spec["flavor"] == "hyvideo"
     Attn = HyAttn if hy else WanAttn
 
-    def call(qq, kk, vv):
+    def call(qq, kk, vv, **extra):
         # step 12 (24 for Wan's doubled counter) is a refresh step: score + select run every call
         if hy:
             return hy_attention(qq, kk, vv, step_idx=12, skip_steps=12, cache_interval=12, layer_idx=0,
                                 sparsity=spec["sparsity"], sparsity_dcrt=0.1, tile_size=16, block_size=128,
-                                video_len=video_len, video_perm=vperm)
+                                video_len=video_len, video_perm=vperm, **extra)
         return wan_attention(qq, kk, vv, step_idx=24, skip_steps=12, cache_interval=12, layer_idx=0,
                              sparsity=spec["sparsity"], sparsity_dcrt=0.1, tile_size=16, block_size=128,
-                             video_perm=vperm)
+                             video_perm=vperm, **extra)
 
-    if seq_layout:
+    if fused_exchange:
+        # shards in symmetric memory; the gather reads peers, the attention epilogue writes peers
+        head_call = call
+        exchange = parallel.SequenceShardExchange(H, L, D, dev)
+        for dst, src in zip(exchange.inputs(), (q_seq, k_seq, v_seq)):
+            dst.copy_(src[0])
+        perm_dev, _ = engine._perm_cache.get(vperm, L, video_len, dev)
+
+        def call(qq, kk, vv):  # noqa: F811  (inputs are the exchange's own shard buffers)
+            return exchange.run(head_call, perm_dev)[None]
+        step_inputs = (q_seq, k_seq, v_seq)
+    elif seq_layout:
         head_call = call
 
         def call(qq, kk, vv):  # noqa: F811  one all-to-all in (Q,K,V together), one out
@@ -403,7 +425,8 @@ def run_gpu(args, spec, rank, local_rank, world):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    secs = timed(lambda: call(*step_inputs), args.steps, barrier)
+    step_ms = []
+    secs = timed(lambda: call(*step_inputs), args.steps, barrier, per_step=step_ms)
     secs = reduce(secs, dist.ReduceOp.MAX if world > 1 else None)
     clocks = sampler.stop() if rank == 0 else None
     ops.check_status(dev)
@@ -465,7 +488,11 @@ def run_gpu(args, spec, rank, local_rank, world):
         host_kw.update(step_idx=24)
 
     def e2e_step():
-        if seq_layout:  # sequence shards: upload, swap, compute, swap back, download
+        if fused_exchange:  # upload straight into the symmetric shard buffers, download the result shard
+            for dst, src in zip(exchange.inputs(), (hq, hk, hv)):
+                dst.copy_(src[0], non_blocking=True)
+            hout.copy_(call(None, None, None), non_blocking=True)
+        elif seq_layout:  # sequence shards: upload, swap, compute, swap back, download
             dq.copy_(hq, non_blocking=True)
             dk.copy_(hk, non_blocking=True)
             dv.copy_(hv, non_blocking=True)
@@ -492,14 +519,17 @@ def run_gpu(args, spec, rank, local_rank, world):
         peak = pk["bf16_tflops_sustained"]
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "ms_per_step_stats": quartiles(step_ms),
+            "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "grid": list(spec["grid"]), "text_tokens": spec["text"],
                        "seq_len": L, "heads": H, "heads_per_gpu": h_local, "head_dim": D,
                        "sparsity": spec["sparsity"], "order": spec.get("order", "hilbert3d"), "block": 128,
                        "tile": 16,
                        "step": "refresh call: permute + score + select + attention (+fused unpermute)",
-                       "parallelism": (f"sequence-sharded x{world}: NCCL all-to-all in and out around "
+                       "parallelism": (f"sequence-sharded x{world}: gather from and scatter to peer shards over "
+                                       f"NVLink inside the permute and attention kernels" if fused_exchange
+                                       else f"sequence-sharded x{world}: NCCL all-to-all in and out around "
                                        f"head-sharded compute" if seq_layout
                                        else f"head-sharded x{world}, no collective"),
                        "l2": "inputs larger than L2 (no flush needed)",
@@ -537,8 +567,10 @@ def main():
     ap.add_argument("--e2e-head-groups", type=int, default=12,
                     help="head groups the host-buffer entry point pipelines its copies over")
     ap.add_argument("--trace-layers", type=int, default=2, help="layers of the *_trace workloads")
-    ap.add_argument("--layout", default="head", choices=["head", "seq"],
-                    help="how inputs arrive at N > 1: head shards (no collective) or sequence shards")
+    ap.add_argument("--layout", default="head", choices=["head", "seq", "seq-fused"],
+                    help="how inputs arrive at N > 1: head shards (no collective), sequence shards swapped by "
+                         "NCCL all-to-alls, or sequence shards in symmetric memory read and written in place "
+                         "by the permute and attention kernels")
     args = ap.parse_args()
     rank, local_rank, world = dist_env()
     spec = dict(WORKLOADS[args.workload])

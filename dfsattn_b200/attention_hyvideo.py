@@ -97,11 +97,13 @@ class DFS_Attention(nn.Module):
 
     def forward(self, q, k, v, attn_mask=None, causal: bool = False, drop_rate: float = 0.0,
                 cu_seqlens_q=None, cu_seqlens_kv=None, max_seqlen_q=None, max_seqlen_kv=None,
-                batch_size: int = 1, prepermuted: bool = False, token_major_out: bool = False) -> torch.Tensor:
+                batch_size: int = 1, prepermuted: bool = False, token_major_out: bool = False,
+                out_shards=None, out_head0: int = 0) -> torch.Tensor:
         """Reference signature plus two switches of the fused processor path: ``prepermuted`` says
         q, k, v already are in the permuted token order (written so by ``ops.qkv_prepare``), and
         ``token_major_out`` stores the result as [L, H, D] memory behind the usual [1, H, L, D]
-        shape."""
+        shape.  ``out_shards`` (an ``ops.ShardTable``) scatters the result to sequence shards on
+        several GPUs instead of returning it (see ``parallel.SequenceShardExchange``)."""
         if causal or drop_rate != 0.0 or attn_mask is not None:
             raise ValueError("the B200 DFS path is non-causal, without dropout or an extra token mask")
         assert batch_size == 1 and q.shape[0] == 1, \
@@ -151,9 +153,12 @@ class DFS_Attention(nn.Module):
 
         t_att = rec.start(device)
         valid = engine.valid_length(cu_seqlens_q, seq_len)
-        out = engine.run_attention(qp, kp, vp, lists, perm, valid, token_major=token_major_out)
+        out = engine.run_attention(qp, kp, vp, lists, perm, valid, token_major=token_major_out,
+                                   out_shards=out_shards, out_head0=out_head0)
         rec.stop(t_att, phase="attention_execution", step_idx=self.step_idx, layer_idx=self.layer_idx,
                  device=device)
+        if out_shards is not None:
+            return None
         return engine.as_reference_layout(out, token_major_out).to(out_dtype)
 
     def _export_mask(self, lists: BlockLists) -> None:
@@ -234,7 +239,8 @@ def dfs_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, step_idx: i
                   max_seqlen_kv=None, sparse_execution: str = "native", hybrid_threshold: int = 8,
                   block_top_p: Optional[float] = None, token_top_k: int = 0, residual_candidate_blocks: int = 4,
                   selector_mode: str = "topk", fine_top_p: float = 0.9, prepermuted: bool = False,
-                  token_major_out: bool = False, **unsupported) -> torch.Tensor:
+                  token_major_out: bool = False, out_shards=None, out_head0: int = 0,
+                  **unsupported) -> torch.Tensor:
     """q, k, v: [1, H, L, D] (raster video tokens, then text).  Returns [1, H, L, D].
 
     Keyword arguments of the reference's other back-ends (``flashinfer64_*``)
@@ -267,4 +273,5 @@ def dfs_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, step_idx: i
         DFS_Attention.set_record_density(True)
     return inst.forward(q=q, k=k, v=v, attn_mask=None, causal=False, drop_rate=0.0, cu_seqlens_q=cu_seqlens_q,
                         cu_seqlens_kv=cu_seqlens_kv, max_seqlen_q=max_seqlen_q, max_seqlen_kv=max_seqlen_kv,
-                        batch_size=q.shape[0], prepermuted=prepermuted, token_major_out=token_major_out)
+                        batch_size=q.shape[0], prepermuted=prepermuted, token_major_out=token_major_out,
+                        out_shards=out_shards, out_head0=out_head0)

@@ -56,7 +56,8 @@ def dfs_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, step_idx: i
                   video_perm: Optional[torch.Tensor] = None, cache_flag: bool = True,
                   record_density: bool = False, cu_seqlens_q=None, cu_seqlens_kv=None, max_seqlen_q=None,
                   max_seqlen_kv=None, sparse_execution: str = "native", hybrid_threshold: int = 8,
-                  prepermuted: bool = False, token_major_out: bool = False, **unsupported) -> torch.Tensor:
+                  prepermuted: bool = False, token_major_out: bool = False, out_shards=None, out_head0: int = 0,
+                  **unsupported) -> torch.Tensor:
     """q, k, v: [1, H, L, D] raster video tokens.  ``step_idx`` is the processor's
     call counter (two calls per denoising step under classifier-free guidance)."""
     for name in unsupported:
@@ -79,4 +80,5 @@ def dfs_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, step_idx: i
         DFS_Attention.set_record_density(True)
     return inst.forward(q=q, k=k, v=v, attn_mask=None, causal=False, drop_rate=0.0, cu_seqlens_q=cu_seqlens_q,
                         cu_seqlens_kv=cu_seqlens_kv, max_seqlen_q=max_seqlen_q, max_seqlen_kv=max_seqlen_kv,
-                        batch_size=q.shape[0], prepermuted=prepermuted, token_major_out=token_major_out)
+                        batch_size=q.shape[0], prepermuted=prepermuted, token_major_out=token_major_out,
+                        out_shards=out_shards, out_head0=out_head0)

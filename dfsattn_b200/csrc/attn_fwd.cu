@@ -71,6 +71,13 @@ struct Params {
   long long kv_len;
   long long out_head_stride;   // elements between heads of the output
   long long out_token_stride;  // elements between tokens of the output
+  // Output scattered over sequence shards held by several GPUs (0 = off): token d goes to shard
+  // d / out_shard_rows, which is [H_total, out_shard_stride rows, D]; this launch's head h is head
+  // out_head0 + h there.  Peer shards are written with plain stores over NVLink.
+  __nv_bfloat16* out_shard[8];
+  long long out_shard_rows;
+  long long out_shard_stride;
+  int out_head0;
   int kmax;
   int q_blocks, k_blocks;
   float scale_log2;
@@ -498,8 +505,17 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (live_a) dst_a = __ldg(p.out_row_map + tok_a);
         if (live_b) dst_b = __ldg(p.out_row_map + tok_b);
       }
-      __nv_bfloat16* out_a = p.out + head * p.out_head_stride + (live_a ? dst_a : 0) * p.out_token_stride;
-      __nv_bfloat16* out_b = p.out + head * p.out_head_stride + (live_b ? dst_b : 0) * p.out_token_stride;
+      __nv_bfloat16 *out_a, *out_b;
+      if (p.out_shard_rows > 0) {
+        const long long ra = live_a ? dst_a : 0, rb = live_b ? dst_b : 0;
+        const long long sa = ra / p.out_shard_rows, sb = rb / p.out_shard_rows;
+        const long long head_row = static_cast<long long>(p.out_head0 + head) * p.out_shard_stride;
+        out_a = p.out_shard[sa] + (head_row + ra - sa * p.out_shard_rows) * HD;
+        out_b = p.out_shard[sb] + (head_row + rb - sb * p.out_shard_rows) * HD;
+      } else {
+        out_a = p.out + head * p.out_head_stride + (live_a ? dst_a : 0) * p.out_token_stride;
+        out_b = p.out + head * p.out_head_stride + (live_b ? dst_b : 0) * p.out_token_stride;
+      }
 #pragma unroll
       for (int h = 0; h < HD / 64; ++h) {
         uint32_t o[32];
@@ -574,10 +590,28 @@ int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& 
 static float* g_debug_buffer = nullptr;
 extern "C" void dfs_debug_set_dump(float* device_buffer) { g_debug_buffer = device_buffer; }
 
-extern "C" int dfs_block_sparse_fwd_ex(const void* q, const void* k, const void* v, const int32_t* idx,
-                                       const int32_t* cnt, int kmax, const int32_t* out_row_map, void* out,
-                                       int out_token_major, int heads, int64_t seq_len, int64_t kv_len,
-                                       int head_dim, float scale, int32_t* status, void* stream_) {
+namespace {
+struct ShardedOut {
+  void* const* shards = nullptr;  // host array of `world` device pointers, or null
+  int world = 0;
+  int64_t shard_rows = 0, shard_stride_rows = 0;
+  int head0 = 0;
+};
+
+int block_sparse_fwd_impl(const void* q, const void* k, const void* v, const int32_t* idx, const int32_t* cnt,
+                          int kmax, const int32_t* out_row_map, void* out, int out_token_major,
+                          const ShardedOut& sh, int heads, int64_t seq_len, int64_t kv_len, int head_dim,
+                          float scale, int32_t* status, void* stream_) {
+  if (sh.shards != nullptr) {
+    if (sh.world <= 0 || sh.world > 8 || sh.head0 < 0) return DFS_ERR_RANGE;
+    if (sh.shard_rows <= 0 || sh.shard_stride_rows < sh.shard_rows || sh.shard_rows * sh.world < seq_len)
+      return DFS_ERR_RANGE;
+    for (int s = 0; s < sh.world; ++s) {
+      if (sh.shards[s] == nullptr) return DFS_ERR_NULL;
+      if (!dfs_aligned16(sh.shards[s])) return DFS_ERR_ALIGN;
+    }
+    out = sh.shards[0];  // only for the shared argument checks below
+  }
   if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return DFS_ERR_NULL;
   if ((idx == nullptr) != (cnt == nullptr)) return DFS_ERR_NULL;
   if (!dfs_aligned16(q) || !dfs_aligned16(k) || !dfs_aligned16(v) || !dfs_aligned16(out)) return DFS_ERR_ALIGN;
@@ -606,12 +640,43 @@ extern "C" int dfs_block_sparse_fwd_ex(const void* q, const void* k, const void*
   // [H, L, D] or, token-major, [L, H*D]
   p.out_head_stride = out_token_major ? head_dim : seq_len * head_dim;
   p.out_token_stride = out_token_major ? static_cast<long long>(heads) * head_dim : head_dim;
+  for (int s = 0; s < 8; ++s)
+    p.out_shard[s] = (sh.shards != nullptr && s < sh.world) ? static_cast<__nv_bfloat16*>(sh.shards[s]) : nullptr;
+  p.out_shard_rows = sh.shards != nullptr ? sh.shard_rows : 0;
+  p.out_shard_stride = sh.shard_stride_rows;
+  p.out_head0 = sh.head0;
   p.kmax = kmax;
   p.q_blocks = static_cast<int>((seq_len + kBlockM - 1) / kBlockM);
   p.k_blocks = static_cast<int>((kv_len + kBlockN - 1) / kBlockN);
   p.scale_log2 = scale * 1.4426950408889634f;
   return head_dim == 128 ? launch_fwd<128>(mq, mk, mv, p, heads, stream)
                          : launch_fwd<64>(mq, mk, mv, p, heads, stream);
+}
+}  // namespace
+
+extern "C" int dfs_block_sparse_fwd_ex(const void* q, const void* k, const void* v, const int32_t* idx,
+                                       const int32_t* cnt, int kmax, const int32_t* out_row_map, void* out,
+                                       int out_token_major, int heads, int64_t seq_len, int64_t kv_len,
+                                       int head_dim, float scale, int32_t* status, void* stream) {
+  return block_sparse_fwd_impl(q, k, v, idx, cnt, kmax, out_row_map, out, out_token_major, ShardedOut(), heads,
+                               seq_len, kv_len, head_dim, scale, status, stream);
+}
+
+extern "C" int dfs_block_sparse_fwd_sharded(const void* q, const void* k, const void* v, const int32_t* idx,
+                                            const int32_t* cnt, int kmax, const int32_t* out_row_map,
+                                            void* const* out_shards, int world, int64_t shard_rows,
+                                            int64_t shard_stride_rows, int head0, int heads, int64_t seq_len,
+                                            int64_t kv_len, int head_dim, float scale, int32_t* status,
+                                            void* stream) {
+  if (out_shards == nullptr) return DFS_ERR_NULL;
+  ShardedOut sh;
+  sh.shards = out_shards;
+  sh.world = world;
+  sh.shard_rows = shard_rows;
+  sh.shard_stride_rows = shard_stride_rows;
+  sh.head0 = head0;
+  return block_sparse_fwd_impl(q, k, v, idx, cnt, kmax, out_row_map, nullptr, 0, sh, heads, seq_len, kv_len,
+                               head_dim, scale, status, stream);
 }
 
 extern "C" int dfs_block_sparse_fwd(const void* q, const void* k, const void* v, const int32_t* idx,

@@ -58,7 +58,73 @@ int launch_permute(const void* const* srcs, void* const* dsts, int n, const int3
   return static_cast<int>(cudaGetLastError());
 }
 
+// ---- gather from sequence shards held by several GPUs ----------------------------------------
+// Source token r lives in shard r / shard_rows (one shard per GPU, [H_total, shard_stride, D]) at
+// local row r % shard_rows; this rank gathers the rows of its own heads [head0, head0 + heads).
+// Peer shards are read with plain 16-byte loads over NVLink; nothing else touches peer memory.
+constexpr int kMaxShards = 8;
+
+struct ShardedArgs {
+  const uint4* src[3][kMaxShards];
+  uint4* dst[3];
+};
+
+__global__ void __launch_bounds__(256)
+    permute_rows_sharded_kernel(const __grid_constant__ ShardedArgs args, const int32_t* __restrict__ perm,
+                                int chunks_per_row, long long chunks_per_head, unsigned shard_rows,
+                                long long shard_stride_chunks, int head0) {
+  const int which = blockIdx.z;
+  const int head = blockIdx.y;
+  uint4* __restrict__ dst = args.dst[which] + static_cast<long long>(head) * chunks_per_head;
+  const long long head_off = static_cast<long long>(head0 + head) * shard_stride_chunks;
+  for (long long c = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; c < chunks_per_head;
+       c += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = c / chunks_per_row;
+    const int col = static_cast<int>(c - row * chunks_per_row);
+    const unsigned from = perm ? static_cast<unsigned>(__ldg(perm + row)) : static_cast<unsigned>(row);
+    const unsigned shard = from / shard_rows;
+    const unsigned local = from - shard * shard_rows;
+    const uint4* __restrict__ src = args.src[which][shard];
+    dst[c] = __ldg(src + head_off + static_cast<long long>(local) * chunks_per_row + col);
+  }
+}
+
 }  // namespace
+
+extern "C" int dfs_permute_qkv_sharded(const void* const* q_shards, const void* const* k_shards,
+                                       const void* const* v_shards, int world, int64_t shard_rows,
+                                       int64_t shard_stride_rows, int head0, const int32_t* perm, void* q_out,
+                                       void* k_out, void* v_out, int heads, int64_t seq_len, int row_bytes,
+                                       void* stream) {
+  if (q_shards == nullptr || k_shards == nullptr || v_shards == nullptr) return DFS_ERR_NULL;
+  if (q_out == nullptr || k_out == nullptr || v_out == nullptr) return DFS_ERR_NULL;
+  if (world <= 0 || world > kMaxShards) return DFS_ERR_RANGE;
+  if (heads <= 0 || head0 < 0 || seq_len <= 0 || row_bytes <= 0 || (row_bytes & 15) != 0) return DFS_ERR_SHAPE;
+  if (shard_rows <= 0 || shard_stride_rows < shard_rows || shard_rows * world < seq_len) return DFS_ERR_RANGE;
+  if (seq_len > 0x7fffffffLL) return DFS_ERR_SHAPE;
+  ShardedArgs args = {};
+  const void* const* tabs[3] = {q_shards, k_shards, v_shards};
+  void* dsts[3] = {q_out, k_out, v_out};
+  for (int t = 0; t < 3; ++t) {
+    if (!dfs_aligned16(dsts[t])) return DFS_ERR_ALIGN;
+    args.dst[t] = static_cast<uint4*>(dsts[t]);
+    for (int s = 0; s < world; ++s) {
+      if (tabs[t][s] == nullptr) return DFS_ERR_NULL;
+      if (!dfs_aligned16(tabs[t][s])) return DFS_ERR_ALIGN;
+      args.src[t][s] = static_cast<const uint4*>(tabs[t][s]);
+    }
+  }
+  const int chunks_per_row = row_bytes / 16;
+  const long long chunks_per_head = static_cast<long long>(seq_len) * chunks_per_row;
+  long long blocks = (chunks_per_head + 255) / 256;
+  const long long cap = 148LL * 8 * 4;
+  if (blocks > cap) blocks = cap;
+  dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(heads), 3);
+  permute_rows_sharded_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      args, perm, chunks_per_row, chunks_per_head, static_cast<unsigned>(shard_rows),
+      shard_stride_rows * chunks_per_row, head0);
+  return static_cast<int>(cudaGetLastError());
+}
 
 extern "C" int dfs_permute_qkv(const void* q, const void* k, const void* v, const int32_t* perm, void* q_out,
                                void* k_out, void* v_out, int heads, int64_t seq_len, int row_bytes,

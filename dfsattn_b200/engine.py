@@ -178,7 +178,7 @@ def valid_length(cu_seqlens, seq_len: int) -> int:
 
 
 def run_attention(qp, kp, vp, lists: Optional[BlockLists], perm_i32, valid_len: int,
-                  token_major: bool = False) -> torch.Tensor:
+                  token_major: bool = False, out_shards=None, out_head0: int = 0) -> torch.Tensor:
     """Block-sparse (or dense when ``lists`` is None) attention on permuted
     bf16 [H,L,D]; returns the un-permuted result, [H,L,D] or, with
     ``token_major``, [L,H,D] (what the output projection reads).
@@ -191,6 +191,12 @@ def run_attention(qp, kp, vp, lists: Optional[BlockLists], perm_i32, valid_len: 
     H, L, D = qp.shape
     idx = lists.idx if lists is not None else None
     cnt = lists.cnt if lists is not None else None
+    if out_shards is not None:
+        # the result is scattered to sequence shards on several GPUs (ops.ShardTable); no local copy
+        if valid_len < L:
+            raise ValueError("a padded tail is not supported together with sharded output")
+        return ops.block_sparse_fwd(qp, kp, vp, idx, cnt, out_row_map=perm_i32, kv_len=valid_len,
+                                    out_shards=out_shards, out_head0=out_head0)
     out = ops.block_sparse_fwd(qp, kp, vp, idx, cnt, out_row_map=perm_i32, kv_len=valid_len,
                                token_major=token_major)
     if valid_len < L:

@@ -10,7 +10,7 @@ from . import engine
 
 def full_attention(q, k, v, mode="flash", drop_rate=0, attn_mask=None, causal=False, cu_seqlens_q=None,
                    cu_seqlens_kv=None, max_seqlen_q=None, max_seqlen_kv=None, batch_size=1, out_row_map=None,
-                   token_major_out=False):
+                   token_major_out=False, out_shards=None, out_head0=0):
     """q, k, v: [1, H, L, D] -> [1, H, L, D] (same layout as the sparse operator).
 
     Two additions for the fused processor path: ``out_row_map`` (int32 [L]) stores the result of
@@ -25,5 +25,8 @@ def full_attention(q, k, v, mode="flash", drop_rate=0, attn_mask=None, causal=Fa
     L = q.shape[2]
     qh, kh, vh = engine.prepare_inputs(q, k, v)
     valid = engine.valid_length(cu_seqlens_kv if cu_seqlens_kv is not None else cu_seqlens_q, L)
-    out = engine.run_attention(qh, kh, vh, None, out_row_map, valid, token_major=token_major_out)
+    out = engine.run_attention(qh, kh, vh, None, out_row_map, valid, token_major=token_major_out,
+                               out_shards=out_shards, out_head0=out_head0)
+    if out_shards is not None:   # scattered to sequence shards on several GPUs (ops.ShardTable)
+        return None
     return engine.as_reference_layout(out, token_major_out).to(out_dtype)

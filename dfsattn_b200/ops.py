@@ -182,8 +182,33 @@ def select_topk(scores, q_rows: int, n_rank: int, k_select: int, dense_row_start
 
 
 # ---- attention -----------------------------------------------------------------------
+class ShardTable:
+    """Where one tensor's sequence shards live on the GPUs of a node: device pointers (one per
+    GPU, peer-accessible), tokens per shard and the row stride of a head inside a shard
+    ([heads_total, stride_rows, D] each).  Passed to the *_sharded entry points as a host array."""
+
+    def __init__(self, ptrs, shard_rows: int, stride_rows: int):
+        import ctypes
+        self.world = len(ptrs)
+        self.array = (ctypes.c_void_p * self.world)(*[int(p) for p in ptrs])
+        self.shard_rows = int(shard_rows)
+        self.stride_rows = int(stride_rows)
+
+
+def permute_qkv_sharded(q_tab: ShardTable, k_tab: ShardTable, v_tab: ShardTable, head0: int, heads: int,
+                        seq_len: int, head_dim: int, perm, device):
+    """Gather this GPU's heads [head0, head0 + heads) of Q, K, V from sequence shards on several GPUs
+    into permuted bf16 [heads, L, D] tensors (``dfs_permute_qkv_sharded``)."""
+    outs = [torch.empty((heads, seq_len, head_dim), dtype=torch.bfloat16, device=device) for _ in range(3)]
+    check(lib.dfs_permute_qkv_sharded(q_tab.array, k_tab.array, v_tab.array, q_tab.world, q_tab.shard_rows,
+                                      q_tab.stride_rows, head0, _ptr(perm), outs[0].data_ptr(),
+                                      outs[1].data_ptr(), outs[2].data_ptr(), heads, seq_len, head_dim * 2,
+                                      _stream(outs[0].device)), "dfs_permute_qkv_sharded")
+    return outs
+
+
 def block_sparse_fwd(q_perm, k_perm, v_perm, idx, cnt, out_row_map=None, kv_len=None, scale=None,
-                     out=None, token_major=False):
+                     out=None, token_major=False, out_shards: Optional[ShardTable] = None, out_head0: int = 0):
     """bf16 block-sparse attention over permuted [H, L, D] tensors; ``idx=None``
     attends every key block (dense).  ``token_major=True`` stores the result as
     [L, H, D] (the layout the output projection reads) instead of [H, L, D]."""
@@ -192,6 +217,15 @@ def block_sparse_fwd(q_perm, k_perm, v_perm, idx, cnt, out_row_map=None, kv_len=
         if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.shape != q_perm.shape:
             raise ValueError("q, k, v must be contiguous bf16 [H, L, D] tensors of one shape")
     H, L, D = q_perm.shape
+    if out_shards is not None:
+        # rows go straight to the sequence shards of the GPUs that own them; nothing is returned
+        check(lib.dfs_block_sparse_fwd_sharded(
+            q_perm.data_ptr(), k_perm.data_ptr(), v_perm.data_ptr(), _ptr(idx), _ptr(cnt),
+            0 if idx is None else idx.shape[-1], _ptr(out_row_map), out_shards.array, out_shards.world,
+            out_shards.shard_rows, out_shards.stride_rows, int(out_head0), H, L,
+            L if kv_len is None else int(kv_len), D, D ** -0.5 if scale is None else float(scale),
+            status_tensor(q_perm.device).data_ptr(), _stream(q_perm.device)), "dfs_block_sparse_fwd_sharded")
+        return None
     want = (L, H, D) if token_major else (H, L, D)
     if out is None:
         out = torch.empty(want, dtype=q_perm.dtype, device=q_perm.device)

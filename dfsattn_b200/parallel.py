@@ -12,6 +12,13 @@ the sequence; the output goes back through one all-to-all.  The collective is
 ``torch.distributed.all_to_all_single`` (NCCL over NVLink on GPUs, gloo in the
 CPU tests); everything a kernel reads has landed in local memory before the
 kernel runs.
+
+``SequenceShardExchange`` is the fused form of the same exchange for the GPUs of
+one node: the shards live in symmetric (peer-accessible) memory, the Hilbert
+gather reads every row straight from the GPU that holds it and the attention
+kernel stores every output row straight into the shard of the GPU that owns it
+-- the two all-to-alls and their staging copies disappear into the gather and
+into the attention epilogue.  Plain loads and stores over NVLink; no multicast.
 """
 from typing import List, Tuple
 
@@ -86,3 +93,54 @@ def dfs_attention_sequence_parallel(q, k, v, seq_len: int, attention_fn, group=N
     qh, kh, vh = seq_to_head_shards([q[0], k[0], v[0]], seq_len, group)
     out = attention_fn(qh[None], kh[None], vh[None])
     return head_to_seq_shards(out[0].contiguous(), H, group)[None]
+
+
+class SequenceShardExchange:
+    """Sequence shards of Q, K, V and of the output in symmetric memory, for the fused exchange.
+
+    Every rank constructs one (collectively), writes its tokens into ``inputs()`` and calls
+    ``run``; afterwards ``output()`` holds its tokens of the result for all heads.  One barrier
+    across the GPUs before the gather (every shard is written) and one after the attention (every
+    row has landed); both are stream-ordered kernels of the symmetric-memory handle, so no host
+    synchronisation happens.
+    """
+
+    def __init__(self, heads: int, seq_len: int, head_dim: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm
+        from . import ops
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.heads, self.seq_len, self.head_dim = heads, seq_len, head_dim
+        self.head0, self.heads_local = head_shard(heads, self.rank, self.world)
+        self.chunk = -(-seq_len // self.world)
+        self.start, self.rows = seq_shard(seq_len, self.rank, self.world)
+        self._in = symm.empty((3, heads, self.chunk, head_dim), dtype=torch.bfloat16, device=device)
+        self._out = symm.empty((heads, self.chunk, head_dim), dtype=torch.bfloat16, device=device)
+        self._h_in = symm.rendezvous(self._in, self.group)
+        self._h_out = symm.rendezvous(self._out, self.group)
+        plane = heads * self.chunk * head_dim * 2   # bytes of one of Q, K, V inside a shard
+        in_ptrs = list(self._h_in.buffer_ptrs)
+        self.in_tabs = [ops.ShardTable([p + t * plane for p in in_ptrs], self.chunk, self.chunk) for t in range(3)]
+        self.out_tab = ops.ShardTable(list(self._h_out.buffer_ptrs), self.chunk, self.chunk)
+
+    def inputs(self):
+        """(q, k, v) views [H, rows, D] of this rank's shard, to be filled by the producer."""
+        return tuple(self._in[t, :, :self.rows] for t in range(3))
+
+    def output(self) -> torch.Tensor:
+        """[H, rows, D] view of this rank's tokens of the result."""
+        return self._out[:, :self.rows]
+
+    def run(self, attention_fn, perm_i32) -> torch.Tensor:
+        """``attention_fn(q, k, v, **kw)`` is a partial of ``dfs_attention`` (or of ``full_attention``
+        wrapped likewise) that accepts ``prepermuted``, ``out_shards`` and ``out_head0``; ``perm_i32``
+        is the int32 device permutation of the whole sequence it will use (None for raster order)."""
+        from . import ops
+        self._h_in.barrier(channel=0)
+        qp, kp, vp = ops.permute_qkv_sharded(*self.in_tabs, self.head0, self.heads_local, self.seq_len,
+                                             self.head_dim, perm_i32, self._in.device)
+        attention_fn(qp[None], kp[None], vp[None], prepermuted=True, out_shards=self.out_tab,
+                     out_head0=self.head0)
+        self._h_out.barrier(channel=0)
+        return self.output()

@@ -14,8 +14,10 @@
  *  - Unless stated otherwise pointers are DEVICE pointers; tensors are dense,
  *    row-major, "head-major" [H, L, D] (the reference's [1,H,L,D] with the
  *    batch of one dropped; attention_hyvideo.py:399 asserts batch 1).
- *  - `stream` is a cudaStream_t passed as void*.  No call synchronises, none
- *    allocates device memory, none keeps global state.
+ *  - `stream` is a cudaStream_t passed as void*.  No call synchronises and none
+ *    allocates device memory.  State kept between calls: host-side lookups that
+ *    are made once (the driver's tensor-map encoder, the per-device address of
+ *    the fixed scratch array of dfs_block_scores_static); nothing else.
  *  - Kernels never trap: every wait inside a kernel is bounded; a kernel that
  *    gives up writes a non-zero code to `*status` (device int32, caller
  *    zero-initialised, may be NULL for kernels that have no waits).
@@ -90,6 +92,38 @@ int dfs_permute_qkv(const void* q, const void* k, const void* v, const int32_t* 
  * itself (out_row_map), which makes this call unnecessary on the hot path. */
 int dfs_unpermute(const void* src, const int32_t* inv_perm, void* dst, int heads,
                   int64_t seq_len, int row_bytes, void* stream);
+
+/* ---- sequence shards on several GPUs (fused with the exchange) -------------- */
+
+/* dfs_permute_qkv for inputs that are sharded along the sequence over `world` GPUs of one node:
+ * the gather reads every row it needs straight from the shard that holds it (plain loads from
+ * peer memory over NVLink), so the Q/K/V all-to-all that would otherwise bring the sequence
+ * together (what Ulysses-style sequence parallelism does before attention) and the Hilbert
+ * gather of dfsattn/attention_hyvideo.py:1034-1036 are one pass.  The reference has no multi-GPU
+ * path for this operator; this is the entry point for callers whose activations are sequence-sharded.
+ *  q/k/v_shards : HOST arrays of `world` DEVICE pointers; shard s holds tokens
+ *                 [s*shard_rows, min((s+1)*shard_rows, L)) of ALL heads as
+ *                 [heads_total, shard_stride_rows, D] (shard_stride_rows >= shard_rows).  Pointers
+ *                 of other GPUs must be peer-accessible (CUDA IPC / symmetric memory).
+ *  head0, heads : this GPU gathers heads [head0, head0 + heads) into q/k/v_out [heads, L, D].
+ *  perm         : int32 [L] (global token order) or NULL for the identity.
+ * The caller orders the launch after every GPU has written its shard (a barrier across GPUs). */
+int dfs_permute_qkv_sharded(const void* const* q_shards, const void* const* k_shards,
+                            const void* const* v_shards, int world, int64_t shard_rows,
+                            int64_t shard_stride_rows, int head0, const int32_t* perm, void* q_out,
+                            void* k_out, void* v_out, int heads, int64_t seq_len, int row_bytes,
+                            void* stream);
+
+/* dfs_block_sparse_fwd whose result goes back to sequence shards on `world` GPUs: the row of
+ * token d (after out_row_map) of local head h is stored in shard d / shard_rows at
+ * [head0 + h, d % shard_rows, :] (plain stores to peer memory), which replaces the output
+ * all-to-all.  out_shards as the input tables above.  The caller makes the other GPUs wait
+ * (a barrier across GPUs) before they read their shard. */
+int dfs_block_sparse_fwd_sharded(const void* q, const void* k, const void* v, const int32_t* idx,
+                                 const int32_t* cnt, int kmax, const int32_t* out_row_map,
+                                 void* const* out_shards, int world, int64_t shard_rows,
+                                 int64_t shard_stride_rows, int head0, int heads, int64_t seq_len,
+                                 int64_t kv_len, int head_dim, float scale, int32_t* status, void* stream);
 
 /* ---- fused pre-attention step (processor side) --------------------------- */
 

@@ -92,3 +92,28 @@ def test_processor_constructors_keep_the_reference_argument_order():
             HP("dfs", 0.3, 16, 128, 1024, None, 5, [0], 12, 12, 0.1, True, **bad)
     with pytest.raises(ValueError):
         HP("dfs", 0.3, 8, 128, 1024, None, 5, [0], 12, 12, 0.1, True)   # tile sizes: 16, 32, 64
+
+
+def test_sharded_entry_points_reject_bad_tables_before_any_launch():
+    # nothing is launched for rejected arguments, so this runs without a GPU
+    from dfsattn_b200 import _lib, ops
+    lib = _lib.lib
+    tab = ops.ShardTable([0x1000, 0x2000], shard_rows=64, stride_rows=64)
+    assert tab.world == 2
+    # null output
+    assert lib.dfs_permute_qkv_sharded(tab.array, tab.array, tab.array, 2, 64, 64, 0, None, None, None, None,
+                                       1, 100, 256, None) == -1
+    # shards do not cover the sequence
+    assert lib.dfs_permute_qkv_sharded(tab.array, tab.array, tab.array, 2, 64, 64, 0, None, 0x3000, 0x4000, 0x5000,
+                                       1, 200, 256, None) == -5
+    # more shards than the table type holds
+    assert lib.dfs_permute_qkv_sharded(tab.array, tab.array, tab.array, 9, 64, 64, 0, None, 0x3000, 0x4000, 0x5000,
+                                       1, 100, 256, None) == -5
+    # a misaligned shard pointer
+    bad = ops.ShardTable([0x1000, 0x2008], shard_rows=64, stride_rows=64)
+    assert lib.dfs_permute_qkv_sharded(bad.array, tab.array, tab.array, 2, 64, 64, 0, None, 0x3000, 0x4000, 0x5000,
+                                       1, 100, 256, None) == -2
+    assert lib.dfs_block_sparse_fwd_sharded(0x1000, 0x1000, 0x1000, None, None, 0, None, None, 2, 64, 64, 0, 1,
+                                            100, 100, 128, 0.1, None, None) == -1
+    assert lib.dfs_block_sparse_fwd_sharded(0x1000, 0x1000, 0x1000, None, None, 0, None, tab.array, 2, 32, 32, 0,
+                                            1, 100, 100, 128, 0.1, None, None) == -5
