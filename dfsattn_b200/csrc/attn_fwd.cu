@@ -7,9 +7,14 @@
 //               (full/empty mbarrier per stage).
 //   warp 1      P.V issuer (one lane): O += P V, tcgen05.mma TS form (P read from
 //               TMEM, V as MN-major B operand).  Owns the TMEM allocation.
-//   warp 2      Q.K^T issuer (one lane): S = Q K^T into one of two TMEM score
-//               buffers, tcgen05.mma SS form, issued two steps ahead of the
-//               softmax.  Two issuing threads instead of one: the tensor pipe's
+//   warp 2      Q.K^T issuer (one lane): S = Q K^T into one of three TMEM score
+//               buffers, tcgen05.mma SS form, up to three steps ahead of the
+//               softmax (a buffer is free again when the P.V that read the P
+//               stored in it has completed).  Three buffers, not two: every
+//               hand-over between the tensor pipe and the softmax costs a few
+//               hundred cycles of latency, and with two steps in flight the pipe
+//               ran out of independent work during those gaps.
+//               Two issuing threads instead of one: the tensor pipe's
 //               issue queue is shallow, so every commit or barrier wait of an
 //               issuing thread is an idle gap in its stream of MMAs; with two
 //               independent streams one fills the other's gaps and the pipe
@@ -17,10 +22,13 @@
 //   warps 4-11  softmax: every warp owns 16 query rows and all 128 score columns
 //               (tcgen05.ld shape 16x256b: a row lives in four threads, so row
 //               maxima and sums are two shuffles and no warp depends on another).
-//               Per step: load the scores, row maxima, exp2 in the log2 domain
-//               with packed fp32x2 arithmetic, P as packed bf16 to TMEM
-//               (tcgen05.st shape 16x128b).  The accumulator O is rescaled in
-//               TMEM only when a row maximum grew by more than 2^8; sum and P
+//               Per step: load the scores, exp2 in the log2 domain with packed
+//               fp32x2 arithmetic against the current reference maximum of the
+//               row while the tile's row maxima are gathered in the same pass,
+//               P as packed bf16 over the first half of the score buffer it
+//               came from (tcgen05.st shape 16x128b).  The reference maximum
+//               moves, and O is rescaled in TMEM, only when a row maximum grew by
+//               more than 2^8 (then the tile is read again and redone); sum and P
 //               use the same reference maximum, so the result is exact.
 //               Epilogue: normalise, store bf16 rows, optionally through a row
 //               map (fused inverse permutation).
@@ -29,7 +37,7 @@
 // Shared memory (HD = 128): Q 32 KB + 3 x 32 KB K stages + 3 x 32 KB V stages.
 // Tiles are stored as [128 rows][64 bf16] boxes with the 128-byte TMA swizzle:
 // the canonical K-major (Q, K) and MN-major (V) tcgen05 operand layout.
-// TMEM (512 columns): S0 | S1 | O | P0 | P1.
+// TMEM (512 columns): S0 | S1 | S2 | O; P(j) lives in the first 64 columns of S[j % 3].
 //
 // Every wait is bounded; on expiry the CTA records DFS_STATUS_WAIT_TIMEOUT,
 // drains its copies and MMAs in flight, frees its TMEM and returns.
@@ -44,7 +52,12 @@ constexpr int kBlockN = 128;  // keys per tile
 constexpr int kThreads = 384;
 constexpr int kStages = 3;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256, kColP0 = 384, kColP1 = 448;
+// Tensor memory: three score buffers of 128 fp32 columns and the output accumulator.  P(j) (packed
+// bf16 pairs, 64 columns) is written over the first half of the score buffer it was computed from:
+// a warp has read all 128 columns of its rows before it stores any, and Q.K^T(j+3) waits for P.V(j).
+constexpr int kSBufs = 3;
+constexpr uint32_t kColO = 384;
+__device__ __forceinline__ uint32_t s_col(int j) { return static_cast<uint32_t>(j % kSBufs) * 128u; }
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 template <int HD>
@@ -55,7 +68,7 @@ struct SmemLayout {
   static constexpr int kKOff = kTileBytes;
   static constexpr int kVOff = kKOff + kStages * kTileBytes;
   static constexpr int kBarOff = kVOff + kStages * kTileBytes;
-  static constexpr int kNumBars = 1 + 4 * kStages + 2 + 2 + 2;
+  static constexpr int kNumBars = 1 + 4 * kStages + kSBufs + kSBufs + 2;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;      // tmem address + two give-up flags
   static constexpr int kTotal = kMiscOff + 16;
 };
@@ -144,6 +157,70 @@ __device__ __forceinline__ uint32_t cvt_bf16x2(float lo, float hi) {
   return d;
 }
 
+// Columns past `valid` of a score tile held as a 16x256b fragment (thread t of a row's four holds
+// columns 8i + 2t, 8i + 2t + 1 of every group i, for two rows) become -inf.
+__device__ __forceinline__ void mask_tail(uint32_t (&r)[64], int valid, int t4) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int col = 8 * i + 2 * t4;
+    if (col >= valid) r[4 * i] = r[4 * i + 2] = __float_as_uint(-INFINITY);
+    if (col + 1 >= valid) r[4 * i + 1] = r[4 * i + 3] = __float_as_uint(-INFINITY);
+  }
+}
+
+// One pass over a thread's share of a score tile (two rows a and b): P = exp2(S*c - m*c) packed as
+// bf16 pairs (P column 4i + t of a row = keys 8i + 2t, 8i + 2t + 1), the tile's partial row sums,
+// and with kTrackMax the thread's share of the tile's raw row maxima.  The first kPoly groups take
+// their exponentials on the FMA pipe.
+template <int kPoly, bool kTrackMax>
+__device__ __forceinline__ void exp_pass(const uint32_t (&r)[64], uint64_t c2, uint64_t nma2, uint64_t nmb2,
+                                         uint32_t (&packed)[32], uint64_t& ta0, uint64_t& ta1, uint64_t& tb0,
+                                         uint64_t& tb1, float& mt_a, float& mt_b) {
+  float xa0 = -INFINITY, xa1 = -INFINITY, xb0 = -INFINITY, xb1 = -INFINITY;
+  ta0 = ta1 = tb0 = tb1 = pack2(0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float sa0 = __uint_as_float(r[4 * i]), sa1 = __uint_as_float(r[4 * i + 1]);
+    const float sb0 = __uint_as_float(r[4 * i + 2]), sb1 = __uint_as_float(r[4 * i + 3]);
+    if (kTrackMax) {
+      if (i & 1) {
+        xa1 = max3(xa1, sa0, sa1);
+        xb1 = max3(xb1, sb0, sb1);
+      } else {
+        xa0 = max3(xa0, sa0, sa1);
+        xb0 = max3(xb0, sb0, sb1);
+      }
+    }
+    const uint64_t xa = fma2(pack2(sa0, sa1), c2, nma2);
+    const uint64_t xb = fma2(pack2(sb0, sb1), c2, nmb2);
+    float a0, a1, b0, b1;
+    if (i < kPoly) {
+      exp2_poly2(xa, a0, a1);
+      exp2_poly2(xb, b0, b1);
+    } else {
+      unpack2(xa, a0, a1);
+      unpack2(xb, b0, b1);
+      a0 = ex2(a0);
+      a1 = ex2(a1);
+      b0 = ex2(b0);
+      b1 = ex2(b1);
+    }
+    if (i & 1) {
+      ta1 = add2(ta1, pack2(a0, a1));
+      tb1 = add2(tb1, pack2(b0, b1));
+    } else {
+      ta0 = add2(ta0, pack2(a0, a1));
+      tb0 = add2(tb0, pack2(b0, b1));
+    }
+    packed[2 * i] = cvt_bf16x2(a0, a1);      // row a (even key in the low half)
+    packed[2 * i + 1] = cvt_bf16x2(b0, b1);  // row b
+  }
+  if (kTrackMax) {
+    mt_a = fmaxf(xa0, xa1);
+    mt_b = fmaxf(xb0, xb1);
+  }
+}
+
 // Of the 16 column groups of a score tile, how many have their exp2 evaluated by the polynomial
 // on the FMA pipe instead of the special-function unit (measured: it pays off only for D = 64,
 // where the tensor work per tile is smaller and the special-function unit is the tighter limit).
@@ -160,6 +237,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                       const __grid_constant__ CUtensorMap tm_v, const Params p) {
   using L = SmemLayout<HD>;
   constexpr int kPolyGroups = HD == 128 ? DFS_POLY_GROUPS_D128 : DFS_POLY_GROUPS_D64;
+  // D = 128: exponentials against the current reference maximum first, row maxima checked afterwards
+  // (one pass in the common case).  D = 64 keeps the separate maximum pass: with half of its exp2 on
+  // the FMA pipe the extra max instructions of the fused pass cost more than the pass they save.
+  constexpr bool kSpeculate = HD == 128;
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need 1024-byte alignment
     if (threadIdx.x == 0 && p.status) atomicExch(p.status, DFS_STATUS_BAD_SMEM_ALIGNMENT);
@@ -177,9 +258,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* k_empty = k_full + kStages;   // [3]  Q.K^T(j) completed: K slot j%3 is free
   uint64_t* v_full = k_empty + kStages;   // [3]  TMA -> P.V issuer
   uint64_t* v_empty = v_full + kStages;   // [3]  P.V(j) completed: V slot j%3 is free and O holds step j
-  uint64_t* s_full = v_empty + kStages;   // [2]  Q.K^T issuer -> softmax: scores of step j are in S[j&1]
-  uint64_t* p_full = s_full + 2;          // [2]  softmax -> both issuers: P(j) is in P[j&1], S[j&1] is free
-  uint64_t* mma_drain = p_full + 2;       // [2]  give-up path of the two issuers
+  uint64_t* s_full = v_empty + kStages;   // [3]  Q.K^T issuer -> softmax: scores of step j are in S[j%3]
+  uint64_t* p_full = s_full + kSBufs;     // [3]  softmax -> P.V issuer: P(j) is in the first half of S[j%3]
+  uint64_t* mma_drain = p_full + kSBufs;  // [2]  give-up path of the two issuers
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -200,11 +281,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kSBufs; ++b) {
       mbar_init(&s_full[b], 1);
       mbar_init(&p_full[b], 8);  // one arrival per softmax warp
-      mbar_init(&mma_drain[b], 1);
     }
+    for (int b = 0; b < 2; ++b) mbar_init(&mma_drain[b], 1);
     abort_flag[0] = 0;  // set by the first wait that expires
     abort_flag[1] = 0;  // separate limit for the drain waits of the give-up path
     fence_barrier_init();
@@ -278,11 +359,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int j = 0; j < n_tiles; ++j) {
         ok = mbar_wait_bounded(&v_full[s], ph, abort_flag);
         if (!ok) break;
-        ok = mbar_wait_bounded(&p_full[j & 1], (j >> 1) & 1, abort_flag);
+        ok = mbar_wait_bounded(&p_full[j % kSBufs], (j / kSBufs) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
         const uint64_t v_desc = v_desc0 + kStageStep * s;
-        const uint32_t p_tmem = tmem_base + ((j & 1) ? kColP1 : kColP0);
+        const uint32_t p_tmem = tmem_base + s_col(j);
         // 16 keys per step: 8 packed columns of P, 16 rows (2 KB = 128 address units) of V
         umma_ts(o_tmem, p_tmem, v_desc, idesc_pv, j > 0);
 #pragma unroll
@@ -313,18 +394,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int j = 0; j < n_tiles && ok; ++j) {
         ok = mbar_wait_bounded(&k_full[s], ph, abort_flag);
         if (!ok) break;
-        if (j >= 2) {
-          // S[j&1] is free once the softmax of step j-2 has read it (it signals together with P)
-          ok = mbar_wait_bounded(&p_full[j & 1], ((j - 2) >> 1) & 1, abort_flag);
-          if (!ok) break;
-          // The softmax of step j will overwrite P[j&1]: P.V(j-2), which reads it, must be
-          // complete before these scores are announced.
-          ok = mbar_wait_bounded(&v_empty[(j - 2) % kStages], ((j - 2) / kStages) & 1, abort_flag);
+        if (j >= kSBufs) {
+          // S[j%3] still holds P(j-3) until P.V(j-3) has completed (which also implies that the
+          // softmax of step j-3 is done with the scores).  The next phase of that barrier is P.V(j),
+          // which needs these very scores: the parity wait cannot be fooled.
+          ok = mbar_wait_bounded(&v_empty[(j - kSBufs) % kStages], ((j - kSBufs) / kStages) & 1, abort_flag);
           if (!ok) break;
         }
         tc_fence_after_sync();
         const uint64_t k_desc = k_desc0 + kStageStep * s;
-        const uint32_t d_tmem = tmem_base + ((j & 1) ? kColS1 : kColS0);
+        const uint32_t d_tmem = tmem_base + s_col(j);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           constexpr uint32_t kBoxStep = L::kBoxBytes >> 4;
@@ -332,7 +411,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           umma_ss(d_tmem, q_desc + off, k_desc + off, idesc_qk, ks > 0);
         }
         umma_commit(&k_empty[s]);
-        umma_commit(&s_full[j & 1]);
+        umma_commit(&s_full[j % kSBufs]);
         if (++s == kStages) {
           s = 0;
           ph ^= 1;
@@ -370,21 +449,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       // keys past kv_len (partial last block, zero-filled by TMA) are masked
       const long long key0 = static_cast<long long>(kb) * kBlockN;
       const int valid = key0 + kBlockN > p.kv_len ? static_cast<int>(p.kv_len - key0) : kBlockN;
-      ok = mbar_wait_bounded(&s_full[j & 1], (j >> 1) & 1, abort_flag);
+      ok = mbar_wait_bounded(&s_full[j % kSBufs], (j / kSBufs) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
 
+      const uint32_t s_addr = tmem_base + lane_sel + s_col(j);
+      const uint32_t p_addr = s_addr;  // P goes over the first half of the scores it came from
       uint32_t r[64];
-      tmem_ld_16x256b_x16(tmem_base + lane_sel + ((j & 1) ? kColS1 : kColS0), r);
+      tmem_ld_16x256b_x16(s_addr, r);
       tmem_wait_ld();
-      if (valid < kBlockN) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int col = 8 * i + 2 * t4;
-          if (col >= valid) r[4 * i] = r[4 * i + 2] = __float_as_uint(-INFINITY);
-          if (col + 1 >= valid) r[4 * i + 1] = r[4 * i + 3] = __float_as_uint(-INFINITY);
-        }
-      }
+      if (valid < kBlockN) mask_tail(r, valid, t4);
       if (dump && j == 0) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -396,23 +470,50 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
 
-      // row maxima: two independent chains per row over this thread's columns, then the row's 4 threads
-      float xa0 = -INFINITY, xa1 = -INFINITY, xb0 = -INFINITY, xb1 = -INFINITY;
+      // The reference maximum of a row moves only when a tile exceeds it by more than the
+      // threshold, which is rare after the first tile.  So the exponentials are taken against the
+      // current reference straight away and the tile's row maxima are gathered in the same pass
+      // (max on the ALU while the special-function unit is the busy one); only when some row of the
+      // warp did exceed the threshold is the tile read again and redone against the new reference.
+      uint32_t packed[32];
+      uint64_t ta0, ta1, tb0, tb1;  // this tile's partial row sums
+      float mt_a = -INFINITY, mt_b = -INFINITY;
+      bool redo = true;  // the exp2 pass against the final reference is still to be done
+      if (kSpeculate && j > 0) {
+        const float nma = -m_a * c, nmb = -m_b * c;  // finite: every row saw a key in the first tile
+        exp_pass<kPolyGroups, true>(r, c2, pack2(nma, nma), pack2(nmb, nmb), packed, ta0, ta1, tb0, tb1, mt_a, mt_b);
+      } else {
+        float xa0 = -INFINITY, xa1 = -INFINITY, xb0 = -INFINITY, xb1 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 16; i += 2) {
-        xa0 = max3(xa0, __uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]));
-        xb0 = max3(xb0, __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-        xa1 = max3(xa1, __uint_as_float(r[4 * i + 4]), __uint_as_float(r[4 * i + 5]));
-        xb1 = max3(xb1, __uint_as_float(r[4 * i + 6]), __uint_as_float(r[4 * i + 7]));
+        for (int i = 0; i < 16; i += 2) {
+          xa0 = max3(xa0, __uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]));
+          xb0 = max3(xb0, __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+          xa1 = max3(xa1, __uint_as_float(r[4 * i + 4]), __uint_as_float(r[4 * i + 5]));
+          xb1 = max3(xb1, __uint_as_float(r[4 * i + 6]), __uint_as_float(r[4 * i + 7]));
+        }
+        mt_a = fmaxf(xa0, xa1);
+        mt_b = fmaxf(xb0, xb1);
       }
-      float mt_a = fmaxf(xa0, xa1), mt_b = fmaxf(xb0, xb1);
       mt_a = fmaxf(mt_a, __shfl_xor_sync(0xffffffffu, mt_a, 1));
       mt_b = fmaxf(mt_b, __shfl_xor_sync(0xffffffffu, mt_b, 1));
       mt_a = fmaxf(mt_a, __shfl_xor_sync(0xffffffffu, mt_a, 2));
       mt_b = fmaxf(mt_b, __shfl_xor_sync(0xffffffffu, mt_b, 2));
-
-      const bool grow = (mt_a - m_a) * c > kRescaleThreshold || (mt_b - m_b) * c > kRescaleThreshold;
-      if (__any_sync(0xffffffffu, grow)) {  // also taken for the first tile
+      bool moved = true;  // some row of the warp needs a new reference (always so in the first tile)
+      if constexpr (!kSpeculate) {
+        const bool grow = (mt_a - m_a) * c > kRescaleThreshold || (mt_b - m_b) * c > kRescaleThreshold;
+        moved = __any_sync(0xffffffffu, grow) != 0;
+      }
+      if (kSpeculate && j > 0) {
+        const bool grow = (mt_a - m_a) * c > kRescaleThreshold || (mt_b - m_b) * c > kRescaleThreshold;
+        redo = __any_sync(0xffffffffu, grow) != 0;
+        if (redo) {
+          tmem_ld_16x256b_x16(s_addr, r);
+          tmem_wait_ld();
+          if (valid < kBlockN) mask_tail(r, valid, t4);
+        }
+      }
+      if (redo) {
+       if (kSpeculate || moved) {
         const float na = fmaxf(m_a, mt_a), nb = fmaxf(m_b, mt_b);
         const float alpha_a = (m_a == -INFINITY) ? 0.f : ex2((m_a - na) * c);
         const float alpha_b = (m_b == -INFINITY) ? 0.f : ex2((m_b - nb) * c);
@@ -444,43 +545,23 @@ __global__ void __launch_bounds__(kThreads, 1)
             tmem_st_16x256b_x8(o_addr + h * 64, o);
           }
         }
+       }
+        // a row whose keys are all masked keeps the reference -inf: its exponentials are exp2(-inf) = 0
+        const float nma = (m_a == -INFINITY) ? 0.f : -m_a * c, nmb = (m_b == -INFINITY) ? 0.f : -m_b * c;
+        float unused_a, unused_b;
+        exp_pass<kPolyGroups, false>(r, c2, pack2(nma, nma), pack2(nmb, nmb), packed, ta0, ta1, tb0, tb1, unused_a,
+                                     unused_b);
       }
-      const float nma = (m_a == -INFINITY) ? 0.f : -m_a * c, nmb = (m_b == -INFINITY) ? 0.f : -m_b * c;
-      const uint64_t nma2 = pack2(nma, nma), nmb2 = pack2(nmb, nmb);
-
-      // P = exp2(S*c - m*c) as packed bf16: P column 4i + t of a row = keys 8i + 2t, 8i + 2t + 1
-      uint32_t packed[32];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const uint64_t xa = fma2(pack2(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1])), c2, nma2);
-        const uint64_t xb = fma2(pack2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), c2, nmb2);
-        float a0, a1, b0, b1;
-        if (i < kPolyGroups) {  // these groups on the FMA pipe
-          exp2_poly2(xa, a0, a1);
-          exp2_poly2(xb, b0, b1);
-        } else {
-          unpack2(xa, a0, a1);
-          unpack2(xb, b0, b1);
-          a0 = ex2(a0);
-          a1 = ex2(a1);
-          b0 = ex2(b0);
-          b1 = ex2(b1);
-        }
-        if (i & 1) {
-          la1 = add2(la1, pack2(a0, a1));
-          lb1 = add2(lb1, pack2(b0, b1));
-        } else {
-          la0 = add2(la0, pack2(a0, a1));
-          lb0 = add2(lb0, pack2(b0, b1));
-        }
-        packed[2 * i] = cvt_bf16x2(a0, a1);      // row a (even key in the low half)
-        packed[2 * i + 1] = cvt_bf16x2(b0, b1);  // row b
-      }
-      tmem_st_16x128b_x16(tmem_base + lane_sel + ((j & 1) ? kColP1 : kColP0), packed);
+      // only now: the scores are not needed any more
+      tmem_st_16x128b_x16(p_addr, packed);
+      la0 = add2(la0, ta0);
+      la1 = add2(la1, ta1);
+      lb0 = add2(lb0, tb0);
+      lb1 = add2(lb1, tb1);
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[j & 1]);
+      if (lane == 0) mbar_arrive(&p_full[j % kSBufs]);
     }
 
     // row sums: this thread's columns, then the row's four threads
