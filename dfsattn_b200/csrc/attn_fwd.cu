@@ -5,20 +5,20 @@
 //   warp 0      TMA producer: the Q tile once, then the K and V tiles of every
 //               listed key block into two 3-stage shared-memory rings
 //               (full/empty mbarrier per stage).
-//   warp 1      P.V issuer (one lane): O += P V, tcgen05.mma TS form (P read from
-//               TMEM, V as MN-major B operand).  Owns the TMEM allocation.
-//   warp 2      Q.K^T issuer (one lane): S = Q K^T into one of three TMEM score
-//               buffers, tcgen05.mma SS form, up to three steps ahead of the
-//               softmax (a buffer is free again when the P.V that read the P
-//               stored in it has completed).  Three buffers, not two: every
-//               hand-over between the tensor pipe and the softmax costs a few
-//               hundred cycles of latency, and with two steps in flight the pipe
-//               ran out of independent work during those gaps.
-//               Two issuing threads instead of one: the tensor pipe's
-//               issue queue is shallow, so every commit or barrier wait of an
-//               issuing thread is an idle gap in its stream of MMAs; with two
-//               independent streams one fills the other's gaps and the pipe
-//               stays busy.
+//   warps 1, 2  MMA issuers (one lane each), warp 1 for the even steps, warp 2 for the
+//               odd ones.  For its step j a thread issues O += P(j) V(j)
+//               (tcgen05.mma TS form: P read from TMEM, V as MN-major B operand)
+//               and straight after it S = Q K(j+3)^T (SS form) into the score
+//               tile that P(j) lives in; the MMAs of one thread execute in issue
+//               order, so that tile is reused without a completion wait.  Three
+//               score tiles, not two: every hand-over between the tensor pipe and
+//               the softmax costs a few hundred cycles of latency, and with two
+//               steps in flight the pipe ran out of independent work during
+//               those gaps.  Two issuing threads instead of one: the tensor
+//               pipe's issue queue is shallow, so every commit or barrier wait
+//               of an issuing thread is an idle gap in its stream of MMAs; with
+//               two independent streams one fills the other's gaps.  Warp 1
+//               owns the TMEM allocation.
 //   warps 4-11  softmax: every warp owns 16 query rows and all 128 score columns
 //               (tcgen05.ld shape 16x256b: a row lives in four threads, so row
 //               maxima and sums are two shuffles and no warp depends on another).
@@ -222,10 +222,11 @@ __device__ __forceinline__ void exp_pass(const uint32_t (&r)[64], uint64_t c2, u
 }
 
 // Of the 16 column groups of a score tile, how many have their exp2 evaluated by the polynomial
-// on the FMA pipe instead of the special-function unit (measured: it pays off only for D = 64,
-// where the tensor work per tile is smaller and the special-function unit is the tighter limit).
+// on the FMA pipe instead of the special-function unit.  Measured: half of them for D = 64, where
+// the tensor work per tile is smaller and the special-function unit is the tighter limit; two of
+// them for D = 128 (the issue slots of the softmax warps are the next limit: 3 and 4 gain less).
 #ifndef DFS_POLY_GROUPS_D128
-#define DFS_POLY_GROUPS_D128 0
+#define DFS_POLY_GROUPS_D128 2
 #endif
 #ifndef DFS_POLY_GROUPS_D64
 #define DFS_POLY_GROUPS_D64 8
@@ -342,65 +343,33 @@ __global__ void __launch_bounds__(kThreads, 1)
           mbar_wait_bounded(&v_full[j % kStages], (j / kStages) & 1, abort_flag + 1);
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ P.V issuer ----------------------------
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------ MMA issuers ----------------------------
+    // Two issuing threads, warp 1 for the even steps and warp 2 for the odd ones.  For its step j a
+    // thread issues P.V(j) and, straight after it, Q.K^T(j+3) into the score tile that P(j) lives
+    // in: tcgen05.mma instructions of one thread execute in the order they were issued, so the
+    // reader of P(j) is ordered before the next writer of that tile without a completion wait (a
+    // wait there left the pipe idle for the ~300 cycles an MMA group needs to report completion).
+    // Two threads because the pipe's issue queue is shallow: the commits and barrier waits of one
+    // thread are idle gaps in its stream of MMAs, which the other thread's stream fills.
     if (lane == 0) {
+      const int par = warp - 1;
       constexpr uint32_t idesc_pv = umma_idesc_bf16(kBlockM, HD, 0, 1);
-      // The descriptor is built once; per stage and per 16-key step it is one 64-bit add
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(kBlockM, kBlockN, 0, 0);
+      // Descriptors are built once; per stage and per 16-element step they are one 64-bit add
       // (the start-address field counts 16-byte units).
       // V tile = HD/64 boxes of [128 keys][64 dims], used as an MN-major operand: 16 KB between
       // the 64-wide groups along the head dimension, 1 KB between groups of 8 keys.
       const uint64_t v_desc0 = umma_desc_sw128(smem_u32(v_ring), L::kBoxBytes, 1024);
-      constexpr uint64_t kStageStep = L::kTileBytes >> 4;
-      const uint32_t o_tmem = tmem_base + kColO;
-      bool ok = true;
-      int s = 0;
-      uint32_t ph = 0;
-      for (int j = 0; j < n_tiles; ++j) {
-        ok = mbar_wait_bounded(&v_full[s], ph, abort_flag);
-        if (!ok) break;
-        ok = mbar_wait_bounded(&p_full[j % kSBufs], (j / kSBufs) & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint64_t v_desc = v_desc0 + kStageStep * s;
-        const uint32_t p_tmem = tmem_base + s_col(j);
-        // 16 keys per step: 8 packed columns of P, 16 rows (2 KB = 128 address units) of V
-        umma_ts(o_tmem, p_tmem, v_desc, idesc_pv, j > 0);
-#pragma unroll
-        for (int ks = 1; ks < kBlockN / 16; ++ks)
-          umma_ts(o_tmem, p_tmem + ks * 8, v_desc + static_cast<uint64_t>(ks * 128), idesc_pv, 1);
-        umma_commit(&v_empty[s]);
-        if (++s == kStages) {
-          s = 0;
-          ph ^= 1;
-        }
-      }
-      if (!ok) {
-        // give-up path: let the MMAs already issued finish before TMEM is freed
-        umma_commit(&mma_drain[0]);
-        mbar_wait_bounded(&mma_drain[0], 0, abort_flag + 1);
-      }
-    }
-  } else if (warp == 2) {
-    // ------------------------------ Q.K^T issuer --------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = umma_idesc_bf16(kBlockM, kBlockN, 0, 0);
       const uint64_t q_desc = umma_desc_sw128(smem_u32(q_tile), 16, 1024);
       const uint64_t k_desc0 = umma_desc_sw128(smem_u32(k_ring), 16, 1024);
       constexpr uint64_t kStageStep = L::kTileBytes >> 4;
+      const uint32_t o_tmem = tmem_base + kColO;
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag);
-      int s = 0;
-      uint32_t ph = 0;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        ok = mbar_wait_bounded(&k_full[s], ph, abort_flag);
-        if (!ok) break;
-        if (j >= kSBufs) {
-          // S[j%3] still holds P(j-3) until P.V(j-3) has completed (which also implies that the
-          // softmax of step j-3 is done with the scores).  The next phase of that barrier is P.V(j),
-          // which needs these very scores: the parity wait cannot be fooled.
-          ok = mbar_wait_bounded(&v_empty[(j - kSBufs) % kStages], ((j - kSBufs) / kStages) & 1, abort_flag);
-          if (!ok) break;
-        }
+
+      auto issue_qk = [&](int j) {   // S[j%3] = Q K(j)^T, K from ring slot j%3
+        const int s = j % kStages;
+        if (!mbar_wait_bounded(&k_full[s], (j / kStages) & 1, abort_flag)) return false;
         tc_fence_after_sync();
         const uint64_t k_desc = k_desc0 + kStageStep * s;
         const uint32_t d_tmem = tmem_base + s_col(j);
@@ -412,14 +381,39 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         umma_commit(&k_empty[s]);
         umma_commit(&s_full[j % kSBufs]);
-        if (++s == kStages) {
-          s = 0;
-          ph ^= 1;
+        return true;
+      };
+
+      // the first three score tiles: 0 and 2 from the even thread, 1 from the odd one
+      for (int j = par; j < kSBufs && j < n_tiles && ok; j += 2) ok = issue_qk(j);
+      for (int j = par; j < n_tiles && ok; j += 2) {
+        const int s = j % kStages;
+        ok = mbar_wait_bounded(&v_full[s], (j / kStages) & 1, abort_flag);
+        if (!ok) break;
+        ok = mbar_wait_bounded(&p_full[j % kSBufs], (j / kSBufs) & 1, abort_flag);
+        if (!ok) break;
+        if (j > 0) {
+          // O += P(j) V(j) follows P.V(j-1), which the other thread issued: wait until that one
+          // has completed (it was issued a step ago; its barrier's next phase is P.V(j+2), issued
+          // by this thread later on, so the parity wait cannot be fooled).
+          ok = mbar_wait_bounded(&v_empty[(j - 1) % kStages], ((j - 1) / kStages) & 1, abort_flag);
+          if (!ok) break;
         }
+        tc_fence_after_sync();
+        const uint64_t v_desc = v_desc0 + kStageStep * s;
+        const uint32_t p_tmem = tmem_base + s_col(j);
+        // 16 keys per step: 8 packed columns of P, 16 rows (2 KB = 128 address units) of V
+        umma_ts(o_tmem, p_tmem, v_desc, idesc_pv, j > 0);
+#pragma unroll
+        for (int ks = 1; ks < kBlockN / 16; ++ks)
+          umma_ts(o_tmem, p_tmem + ks * 8, v_desc + static_cast<uint64_t>(ks * 128), idesc_pv, 1);
+        umma_commit(&v_empty[s]);
+        if (j + kSBufs < n_tiles) ok = issue_qk(j + kSBufs);
       }
       if (!ok) {
-        umma_commit(&mma_drain[1]);
-        mbar_wait_bounded(&mma_drain[1], 0, abort_flag + 1);
+        // give-up path: let the MMAs already issued finish before TMEM is freed
+        umma_commit(&mma_drain[par]);
+        mbar_wait_bounded(&mma_drain[par], 0, abort_flag + 1);
       }
     }
   } else if (warp >= 4) {
