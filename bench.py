@@ -36,6 +36,7 @@ WORKLOADS = {
     "wan_480p_h8": dict(grid=(21, 30, 52), text=0, heads=8, dim=128, sparsity=0.3, flavor="wan"),
     "hunyuan_480p_h4": dict(grid=(33, 30, 45), text=256, heads=4, dim=128, sparsity=0.3, flavor="hyvideo"),
     "tiny": dict(grid=(4, 16, 16), text=0, heads=2, dim=64, sparsity=0.3, flavor="hyvideo"),
+    "tiny_wan": dict(grid=(4, 16, 16), text=0, heads=2, dim=128, sparsity=0.3, flavor="wan"),
     # the mask-caching trace: 50 denoising steps (12 dense, refreshes at 12 / 24 / 36 with sparsity
     # 0.3 / 0.2 / 0.1) over --trace-layers layers with drifting Q/K; one bench step = the whole trace
     "hunyuan_720p_trace": dict(grid=(33, 45, 80), text=256, heads=24, dim=128, sparsity=0.3, flavor="hyvideo",
@@ -65,8 +66,48 @@ class ClockSampler:
         self.rows = []
         self.proc = None
         self.gpu_index = gpu_index
+        self.nvml = None
+        self._stop = threading.Event()
+
+    # NVML read directly (a sample every ~10 ms: short timed regions are covered too); nvidia-smi as a
+    # subprocess when the NVML binding is not importable.  Reading only: nothing is ever set.
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.gpu_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+
+    def _poll_nvml(self):
+        nv, h = self.nvml
+        bits = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
+                "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
+                "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+        mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+        while not self._stop.is_set():
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                pw = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                self.rows.append([str(sm), str(mx), str(pw)] +
+                                 ["Active" if mask & bit else "Not Active" for bit in bits.values()])
+            except Exception:
+                pass
+            self._stop.wait(0.01)
 
     def start(self):
+        try:
+            self.nvml = self._nvml_handle()
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
@@ -81,13 +122,17 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
-        if self.proc is None:
+        if self.nvml is not None:
+            self._stop.set()
+            self.thread.join(timeout=2)
+        elif self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
+        else:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
         sm, mx, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in self.rows:
@@ -102,7 +147,8 @@ class ClockSampler:
                     reasons.add(n)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons),
+                "source": "nvml" if self.nvml is not None else "nvidia-smi"}
 
 
 def dist_env():
@@ -473,6 +519,24 @@ def run_gpu(args, spec, rank, local_rank, world):
     stages["fused_prepare_ms"] = 1e3 * t_prep
     stages["fused_prepare_gbs"] = 6 * tensor_bytes / t_prep / 1e9
     del src, ang, tabs
+
+    if not hy and not seq_layout:
+        # Both guidance passes of a Wan denoising step (a reuse step: lists cached): two operator calls
+        # one after the other, as the reference runs them, against the one batched call.
+        from dfsattn_b200.attention_wan import dfs_attention_cfg_pair
+        wkw = dict(skip_steps=12, cache_interval=12, layer_idx=0, sparsity=spec["sparsity"], sparsity_dcrt=0.1,
+                   tile_size=16, block_size=128, video_perm=vperm)
+        q2, k2, v2 = (torch.cat([t, t.flip(1)]) for t in (q, k, v))
+
+        def two_calls():
+            wan_attention(q2[0:1], k2[0:1], v2[0:1], step_idx=26, **wkw)
+            wan_attention(q2[1:2], k2[1:2], v2[1:2], step_idx=27, **wkw)
+        t_two = timed(two_calls, n_stage, barrier, warm=2) / n_stage
+        t_pair = timed(lambda: dfs_attention_cfg_pair(q2, k2, v2, step_idx=26, **wkw), n_stage, barrier,
+                       warm=2) / n_stage
+        stages["cfg_two_calls_ms"] = 1e3 * reduce(t_two, dist.ReduceOp.MAX if world > 1 else None)
+        stages["cfg_pair_call_ms"] = 1e3 * reduce(t_pair, dist.ReduceOp.MAX if world > 1 else None)
+        del q2, k2, v2
 
     # ---- end to end through the public API with HOST buffers ----------------
     hq, hk, hv = (t.cpu().pin_memory() for t in step_inputs)

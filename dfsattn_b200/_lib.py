@@ -36,6 +36,9 @@ SIGNATURES = {
     "dfs_block_sparse_fwd_ex": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                         c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_float, c_void_p,
                                         c_void_p]),
+    "dfs_block_sparse_fwd_batched": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                             c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int, c_float,
+                                             c_void_p, c_void_p]),
     "dfs_permute_qkv_sharded": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p,
                                         c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_void_p]),
     "dfs_block_sparse_fwd_sharded": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,

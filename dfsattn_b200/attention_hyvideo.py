@@ -142,14 +142,7 @@ class DFS_Attention(nn.Module):
             self._export_mask(lists)
 
         if cls.record_density:
-            pairs = ops.interaction_count(lists.idx, lists.cnt, lists.idx.shape[0], seq_len, self.block_size)
-            total = lists.idx.shape[0] * seq_len * seq_len
-            cls.density_records.setdefault(self.step_idx, {})[self.layer_idx] = pairs / total
-            cls.sparsity_records.setdefault(self.step_idx, {})[self.layer_idx] = {
-                "block_density": pairs / total, "realized_block_sparsity": 1.0 - pairs / total,
-                "residual_token_interactions": 0.0, "final_density": pairs / total,
-                "final_hybrid_sparsity": 1.0 - pairs / total,
-            }
+            self._record_density(lists, seq_len)
 
         t_att = rec.start(device)
         valid = engine.valid_length(cu_seqlens_q, seq_len)
@@ -160,6 +153,17 @@ class DFS_Attention(nn.Module):
         if out_shards is not None:
             return None
         return engine.as_reference_layout(out, token_major_out).to(out_dtype)
+
+    def _record_density(self, lists: BlockLists, seq_len: int) -> None:
+        cls = type(self)
+        pairs = ops.interaction_count(lists.idx, lists.cnt, lists.idx.shape[0], seq_len, self.block_size)
+        total = lists.idx.shape[0] * seq_len * seq_len
+        cls.density_records.setdefault(self.step_idx, {})[self.layer_idx] = pairs / total
+        cls.sparsity_records.setdefault(self.step_idx, {})[self.layer_idx] = {
+            "block_density": pairs / total, "realized_block_sparsity": 1.0 - pairs / total,
+            "residual_token_interactions": 0.0, "final_density": pairs / total,
+            "final_hybrid_sparsity": 1.0 - pairs / total,
+        }
 
     def _export_mask(self, lists: BlockLists) -> None:
         """Headless replacement of the PNG heat-maps: one .npy bool mask per head."""

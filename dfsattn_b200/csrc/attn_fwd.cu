@@ -91,6 +91,10 @@ struct Params {
   long long out_shard_rows;
   long long out_shard_stride;
   int out_head0;
+  // Batched launch: the grid's heads are `batch` groups of list_heads heads each; head h reads the
+  // lists of head h % list_heads and writes group h / list_heads of the output.
+  int list_heads;
+  long long out_batch_stride;  // elements between two groups of the output
   int kmax;
   int q_blocks, k_blocks;
   float scale_log2;
@@ -269,10 +273,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int lane = threadIdx.x & 31;
   // heavy rows (the dense text rows sit at the end) are scheduled first
   const int qb = p.q_blocks - 1 - static_cast<int>(blockIdx.x);
-  const int head = blockIdx.y;
-  const int n_tiles = p.idx ? p.cnt[static_cast<size_t>(head) * p.q_blocks + qb] : p.k_blocks;
+  const int head = blockIdx.y;                 // row of the Q/K/V tensors
+  const int group = head / p.list_heads;       // batch element
+  const int lhead = head - group * p.list_heads;  // head within the batch element: lists and output
+  const int n_tiles = p.idx ? p.cnt[static_cast<size_t>(lhead) * p.q_blocks + qb] : p.k_blocks;
   const int32_t* __restrict__ my_idx =
-      p.idx ? p.idx + (static_cast<size_t>(head) * p.q_blocks + qb) * p.kmax : nullptr;
+      p.idx ? p.idx + (static_cast<size_t>(lhead) * p.q_blocks + qb) * p.kmax : nullptr;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -588,8 +594,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         out_a = p.out_shard[sa] + (head_row + ra - sa * p.out_shard_rows) * HD;
         out_b = p.out_shard[sb] + (head_row + rb - sb * p.out_shard_rows) * HD;
       } else {
-        out_a = p.out + head * p.out_head_stride + (live_a ? dst_a : 0) * p.out_token_stride;
-        out_b = p.out + head * p.out_head_stride + (live_b ? dst_b : 0) * p.out_token_stride;
+        __nv_bfloat16* base = p.out + group * p.out_batch_stride + lhead * p.out_head_stride;
+        out_a = base + (live_a ? dst_a : 0) * p.out_token_stride;
+        out_b = base + (live_b ? dst_b : 0) * p.out_token_stride;
       }
 #pragma unroll
       for (int h = 0; h < HD / 64; ++h) {
@@ -675,9 +682,13 @@ struct ShardedOut {
 
 int block_sparse_fwd_impl(const void* q, const void* k, const void* v, const int32_t* idx, const int32_t* cnt,
                           int kmax, const int32_t* out_row_map, void* out, int out_token_major,
-                          const ShardedOut& sh, int heads, int64_t seq_len, int64_t kv_len, int head_dim,
-                          float scale, int32_t* status, void* stream_) {
+                          const ShardedOut& sh, int batch, int heads, int64_t seq_len, int64_t kv_len,
+                          int head_dim, float scale, int32_t* status, void* stream_) {
+  // `heads` = heads of one batch element (what the lists cover); the tensors hold batch * heads heads
+  if (batch <= 0 || heads <= 0 || static_cast<int64_t>(batch) * heads > 65535) return DFS_ERR_SHAPE;
+  const int all_heads = batch * heads;
   if (sh.shards != nullptr) {
+    if (batch != 1) return DFS_ERR_RANGE;
     if (sh.world <= 0 || sh.world > 8 || sh.head0 < 0) return DFS_ERR_RANGE;
     if (sh.shard_rows <= 0 || sh.shard_stride_rows < sh.shard_rows || sh.shard_rows * sh.world < seq_len)
       return DFS_ERR_RANGE;
@@ -691,16 +702,16 @@ int block_sparse_fwd_impl(const void* q, const void* k, const void* v, const int
   if ((idx == nullptr) != (cnt == nullptr)) return DFS_ERR_NULL;
   if (!dfs_aligned16(q) || !dfs_aligned16(k) || !dfs_aligned16(v) || !dfs_aligned16(out)) return DFS_ERR_ALIGN;
   if (head_dim != 64 && head_dim != 128) return DFS_ERR_SHAPE;
-  if (heads <= 0 || heads > 65535 || seq_len <= 0) return DFS_ERR_SHAPE;
+  if (seq_len <= 0) return DFS_ERR_SHAPE;
   if (kv_len <= 0 || kv_len > seq_len) return DFS_ERR_RANGE;
   if (idx != nullptr && kmax <= 0) return DFS_ERR_RANGE;
   if (!(scale > 0.f)) return DFS_ERR_RANGE;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 
   CUtensorMap mq, mk, mv;
-  int rc = make_tile_map(&mq, q, heads, seq_len, head_dim);
-  if (rc == 0) rc = make_tile_map(&mk, k, heads, seq_len, head_dim);
-  if (rc == 0) rc = make_tile_map(&mv, v, heads, seq_len, head_dim);
+  int rc = make_tile_map(&mq, q, all_heads, seq_len, head_dim);
+  if (rc == 0) rc = make_tile_map(&mk, k, all_heads, seq_len, head_dim);
+  if (rc == 0) rc = make_tile_map(&mv, v, all_heads, seq_len, head_dim);
   if (rc != 0) return rc;
 
   Params p;
@@ -712,9 +723,11 @@ int block_sparse_fwd_impl(const void* q, const void* k, const void* v, const int
   p.debug = g_debug_buffer;
   p.seq_len = seq_len;
   p.kv_len = kv_len;
-  // [H, L, D] or, token-major, [L, H*D]
+  // per batch element [H, L, D] or, token-major, [L, H*D]
   p.out_head_stride = out_token_major ? head_dim : seq_len * head_dim;
   p.out_token_stride = out_token_major ? static_cast<long long>(heads) * head_dim : head_dim;
+  p.list_heads = heads;
+  p.out_batch_stride = static_cast<long long>(heads) * seq_len * head_dim;
   for (int s = 0; s < 8; ++s)
     p.out_shard[s] = (sh.shards != nullptr && s < sh.world) ? static_cast<__nv_bfloat16*>(sh.shards[s]) : nullptr;
   p.out_shard_rows = sh.shards != nullptr ? sh.shard_rows : 0;
@@ -724,8 +737,8 @@ int block_sparse_fwd_impl(const void* q, const void* k, const void* v, const int
   p.q_blocks = static_cast<int>((seq_len + kBlockM - 1) / kBlockM);
   p.k_blocks = static_cast<int>((kv_len + kBlockN - 1) / kBlockN);
   p.scale_log2 = scale * 1.4426950408889634f;
-  return head_dim == 128 ? launch_fwd<128>(mq, mk, mv, p, heads, stream)
-                         : launch_fwd<64>(mq, mk, mv, p, heads, stream);
+  return head_dim == 128 ? launch_fwd<128>(mq, mk, mv, p, all_heads, stream)
+                         : launch_fwd<64>(mq, mk, mv, p, all_heads, stream);
 }
 }  // namespace
 
@@ -733,8 +746,17 @@ extern "C" int dfs_block_sparse_fwd_ex(const void* q, const void* k, const void*
                                        const int32_t* cnt, int kmax, const int32_t* out_row_map, void* out,
                                        int out_token_major, int heads, int64_t seq_len, int64_t kv_len,
                                        int head_dim, float scale, int32_t* status, void* stream) {
-  return block_sparse_fwd_impl(q, k, v, idx, cnt, kmax, out_row_map, out, out_token_major, ShardedOut(), heads,
+  return block_sparse_fwd_impl(q, k, v, idx, cnt, kmax, out_row_map, out, out_token_major, ShardedOut(), 1, heads,
                                seq_len, kv_len, head_dim, scale, status, stream);
+}
+
+extern "C" int dfs_block_sparse_fwd_batched(const void* q, const void* k, const void* v, const int32_t* idx,
+                                            const int32_t* cnt, int kmax, const int32_t* out_row_map, void* out,
+                                            int out_token_major, int batch, int heads, int64_t seq_len,
+                                            int64_t kv_len, int head_dim, float scale, int32_t* status,
+                                            void* stream) {
+  return block_sparse_fwd_impl(q, k, v, idx, cnt, kmax, out_row_map, out, out_token_major, ShardedOut(), batch,
+                               heads, seq_len, kv_len, head_dim, scale, status, stream);
 }
 
 extern "C" int dfs_block_sparse_fwd_sharded(const void* q, const void* k, const void* v, const int32_t* idx,
@@ -750,7 +772,7 @@ extern "C" int dfs_block_sparse_fwd_sharded(const void* q, const void* k, const 
   sh.shard_rows = shard_rows;
   sh.shard_stride_rows = shard_stride_rows;
   sh.head0 = head0;
-  return block_sparse_fwd_impl(q, k, v, idx, cnt, kmax, out_row_map, nullptr, 0, sh, heads, seq_len, kv_len,
+  return block_sparse_fwd_impl(q, k, v, idx, cnt, kmax, out_row_map, nullptr, 0, sh, 1, heads, seq_len, kv_len,
                                head_dim, scale, status, stream);
 }
 

@@ -21,8 +21,9 @@ from . import engine, ops
 _table_cache = {}
 
 
-def eligible(hidden_states: torch.Tensor, heads: int, width: int) -> bool:
-    return (hidden_states.is_cuda and hidden_states.dtype == torch.bfloat16 and hidden_states.shape[0] == 1
+def eligible(hidden_states: torch.Tensor, heads: int, width: int, max_batch: int = 1) -> bool:
+    return (hidden_states.is_cuda and hidden_states.dtype == torch.bfloat16
+            and 1 <= hidden_states.shape[0] <= max_batch
             and width % heads == 0 and width // heads in (64, 128))
 
 

@@ -208,15 +208,40 @@ def permute_qkv_sharded(q_tab: ShardTable, k_tab: ShardTable, v_tab: ShardTable,
 
 
 def block_sparse_fwd(q_perm, k_perm, v_perm, idx, cnt, out_row_map=None, kv_len=None, scale=None,
-                     out=None, token_major=False, out_shards: Optional[ShardTable] = None, out_head0: int = 0):
+                     out=None, token_major=False, out_shards: Optional[ShardTable] = None, out_head0: int = 0,
+                     batch: int = 1):
     """bf16 block-sparse attention over permuted [H, L, D] tensors; ``idx=None``
     attends every key block (dense).  ``token_major=True`` stores the result as
-    [L, H, D] (the layout the output projection reads) instead of [H, L, D]."""
+    [L, H, D] (the layout the output projection reads) instead of [H, L, D].
+
+    ``batch`` > 1: the tensors are [batch * H, L, D], the lists [H, Qb, kmax] are shared by all
+    batch elements, and the result is [batch, H, L, D] or, token-major, [batch, L, H, D]
+    (``dfs_block_sparse_fwd_batched``)."""
     _need_cuda(q_perm, k_perm, v_perm)
     for t in (q_perm, k_perm, v_perm):
         if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.shape != q_perm.shape:
             raise ValueError("q, k, v must be contiguous bf16 [H, L, D] tensors of one shape")
     H, L, D = q_perm.shape
+    batch = int(batch)
+    if batch < 1 or H % batch:
+        raise ValueError("the leading dimension must be batch * heads")
+    if batch > 1:
+        if out_shards is not None:
+            raise ValueError("batched launches do not scatter to sequence shards")
+        H //= batch
+        if idx is not None and idx.shape[0] != H:
+            raise ValueError("batched launches take one list per head of ONE batch element")
+        want = (batch, L, H, D) if token_major else (batch, H, L, D)
+        if out is None:
+            out = torch.empty(want, dtype=q_perm.dtype, device=q_perm.device)
+        elif tuple(out.shape) != want or not out.is_contiguous() or out.dtype != torch.bfloat16:
+            raise ValueError(f"out must be a contiguous bf16 tensor of shape {want}")
+        check(lib.dfs_block_sparse_fwd_batched(
+            q_perm.data_ptr(), k_perm.data_ptr(), v_perm.data_ptr(), _ptr(idx), _ptr(cnt),
+            0 if idx is None else idx.shape[-1], _ptr(out_row_map), out.data_ptr(), int(token_major), batch, H, L,
+            L if kv_len is None else int(kv_len), D, D ** -0.5 if scale is None else float(scale),
+            status_tensor(q_perm.device).data_ptr(), _stream(q_perm.device)), "dfs_block_sparse_fwd_batched")
+        return out
     if out_shards is not None:
         # rows go straight to the sequence shards of the GPUs that own them; nothing is returned
         check(lib.dfs_block_sparse_fwd_sharded(

@@ -6,6 +6,12 @@ same constructor argument order and ``__call__`` signature.  Self-attention
 counter advances twice per denoising step (classifier-free guidance) and wraps
 at 100 (:320-323).  Cross-attention (``cross_flag=True``) is always dense and
 uses PyTorch SDPA because its key length differs from its query length.
+
+One addition: a self-attention call with a batch of TWO is taken as both
+guidance passes of one denoising step (conditional first), counts as two calls
+and runs as one gather and one attention launch with shared index lists
+(``attention_wan.dfs_attention_cfg_pair``); the reference's operator refuses a
+batch (dfsattn/attention_wan.py:219), so its callers run the passes one by one.
 """
 from typing import Optional
 
@@ -13,7 +19,7 @@ import torch
 import torch.nn.functional as F
 
 from . import fused_qkv
-from .attention_wan import dfs_attention
+from .attention_wan import dfs_attention, dfs_attention_cfg_pair
 from .fullattention import full_attention
 
 
@@ -76,41 +82,85 @@ class Wan_DFSAttn_Processor2_0:
             return "sparse"
         return "dense"
 
+    def _advance(self, calls: int = 1) -> None:
+        for _ in range(calls):
+            self.step_idx += 1
+            if self.step_idx == self.num_inference_steps * 2:
+                self.step_idx = 0
+
+    def _dfs_kwargs(self, S_q: int, S_k: int) -> dict:
+        return dict(skip_steps=self.skip_steps, cache_interval=self.cache_interval, layer_idx=self.layer_idx,
+                    sparsity=self.sparsity, sparsity_dcrt=self.sparsity_dcrt, tile_size=self.tile_size,
+                    block_size=self.block_size, video_perm=self.video_perm, cache_flag=self.cache_flag,
+                    record_density=self.record_density, max_seqlen_q=S_q, max_seqlen_kv=S_k,
+                    sparse_execution=self.sparse_execution, hybrid_threshold=self.hybrid_threshold)
+
+    # A batch of two sparse guidance passes as one gather + one attention launch (True), or as two
+    # operator calls one after the other (False); the results are the same bits either way.
+    cfg_pair_batch = True
+
+    def _attend_self(self, query, key, value, perm=None, fused: bool = False):
+        """Self-attention of one pass ([1, H, S, D]) or of both guidance passes ([2, H, S, D]) per the
+        gate; advances the call counter by the batch.  ``fused``: inputs are already in the permuted
+        token order ``perm`` and the result is wanted token-major."""
+        B, _, S, _ = query.shape
+        extra = dict(prepermuted=True, token_major_out=True) if fused else {}
+        if B == 2:
+            if self.step_idx % 2:
+                raise ValueError("a batch of two guidance passes must start at an even call counter")
+            first = self._gate()
+            self.step_idx += 1
+            second = self._gate()
+            self.step_idx -= 1
+            if self.cfg_pair_batch and first == second == "sparse":
+                out = dfs_attention_cfg_pair(query, key, value, step_idx=self.step_idx,
+                                             **self._dfs_kwargs(S, S), **extra)
+                self._advance(2)
+                return out
+        elif B != 1:
+            raise AssertionError("DFS Attention with block sparse currently supports batch size 1 "
+                                 "(or 2: the guidance pair).")
+        outs = []
+        for b in range(B):
+            qb, kb, vb = (t[b:b + 1] for t in (query, key, value))
+            if self._gate() == "sparse":
+                outs.append(dfs_attention(qb, kb, vb, step_idx=self.step_idx, **self._dfs_kwargs(S, S), **extra))
+            elif fused:
+                outs.append(full_attention(qb, kb, vb, mode="flash", max_seqlen_q=S, max_seqlen_kv=S,
+                                           batch_size=1, out_row_map=perm, token_major_out=True))
+            else:
+                outs.append(full_attention(qb, kb, vb, mode="flash", max_seqlen_q=S, max_seqlen_kv=S,
+                                           batch_size=1))
+            self._advance()
+        return outs[0] if B == 1 else torch.cat(outs, dim=0)
+
     # One pass from the projections to permuted, normalised, rotated Q/K/V and a token-major
     # attention result; class-wide switch, self-attention only (cross-attention is not on the path).
     fused_prepare = True
 
     def _fused_self_attention(self, attn, hidden_states, rotary_emb):
         width = getattr(attn.to_q, "out_features", None)
-        if width is None or not fused_qkv.eligible(hidden_states, attn.heads, width):
+        if width is None or not fused_qkv.eligible(hidden_states, attn.heads, width, max_batch=2):
             return None
-        S = hidden_states.shape[1]
+        B, S = hidden_states.shape[0], hidden_states.shape[1]
         try:
             perm = fused_qkv.token_perm(self.video_perm, S, S, hidden_states.device) \
                 if self.video_perm is not None else None
-            out = fused_qkv.prepare(attn.to_q(hidden_states), attn.to_k(hidden_states), attn.to_v(hidden_states),
-                                    attn.heads, getattr(attn, "norm_q", None), getattr(attn, "norm_k", None),
-                                    rotary_emb, S, perm)
+            pq, pk, pv = attn.to_q(hidden_states), attn.to_k(hidden_states), attn.to_v(hidden_states)
+            H, D = attn.heads, width // attn.heads
+            out = tuple(torch.empty((B * H, S, D), dtype=torch.bfloat16, device=hidden_states.device)
+                        for _ in range(3))
+            for b in range(B):   # one pass per batch element, each filling its heads of the shared buffers
+                fused_qkv.prepare(pq[b], pk[b], pv[b], H, getattr(attn, "norm_q", None),
+                                  getattr(attn, "norm_k", None), rotary_emb, S, perm,
+                                  out=tuple(t[b * H:(b + 1) * H] for t in out))
         except TypeError:
             return None
-        query, key, value = (t.unsqueeze(0) for t in out)
-        if self._gate() == "sparse":
-            hidden_states = dfs_attention(
-                query, key, value, step_idx=self.step_idx, skip_steps=self.skip_steps,
-                cache_interval=self.cache_interval, layer_idx=self.layer_idx, sparsity=self.sparsity,
-                sparsity_dcrt=self.sparsity_dcrt, tile_size=self.tile_size, block_size=self.block_size,
-                video_perm=self.video_perm, cache_flag=self.cache_flag, record_density=self.record_density,
-                max_seqlen_q=S, max_seqlen_kv=S, sparse_execution=self.sparse_execution,
-                hybrid_threshold=self.hybrid_threshold, prepermuted=True, token_major_out=True)
-        else:
-            hidden_states = full_attention(query, key, value, mode="flash", max_seqlen_q=S, max_seqlen_kv=S,
-                                           batch_size=1, out_row_map=perm, token_major_out=True)
+        query, key, value = (t.view(B, H, S, D) for t in out)
+        hidden_states = self._attend_self(query, key, value, perm=perm, fused=True)
         hidden_states = hidden_states.transpose(1, 2).flatten(2, 3).type_as(query)  # a view
         hidden_states = attn.to_out[0](hidden_states)
         hidden_states = attn.to_out[1](hidden_states)
-        self.step_idx += 1
-        if self.step_idx == self.num_inference_steps * 2:
-            self.step_idx = 0
         return hidden_states
 
     def __call__(self, attn, hidden_states: torch.Tensor, encoder_hidden_states: Optional[torch.Tensor] = None,
@@ -157,28 +207,26 @@ class Wan_DFSAttn_Processor2_0:
             hidden_states_img = hidden_states_img.transpose(1, 2).flatten(2, 3).type_as(query)
 
         S_q, S_k = query.shape[2], key.shape[2]
-        gate = self._gate()
-        if gate == "sparse":
-            hidden_states = dfs_attention(
-                query, key, value, step_idx=self.step_idx, skip_steps=self.skip_steps,
-                cache_interval=self.cache_interval, layer_idx=self.layer_idx, sparsity=self.sparsity,
-                sparsity_dcrt=self.sparsity_dcrt, tile_size=self.tile_size, block_size=self.block_size,
-                video_perm=self.video_perm, cache_flag=self.cache_flag, record_density=self.record_density,
-                max_seqlen_q=S_q, max_seqlen_kv=S_k, sparse_execution=self.sparse_execution,
-                hybrid_threshold=self.hybrid_threshold)
-        elif S_q == S_k and attention_mask is None:
-            hidden_states = full_attention(query, key, value, mode="flash", max_seqlen_q=S_q, max_seqlen_kv=S_k,
-                                           batch_size=query.shape[0])
-        else:  # cross-attention: different key length, not part of the DFS path
-            hidden_states = F.scaled_dot_product_attention(query, key, value)
+        if self_attention and attention_mask is None:
+            hidden_states = self._attend_self(query, key, value)   # advances the counter
+            counted = True
+        else:
+            counted = False
+            gate = self._gate()
+            if gate == "sparse":
+                hidden_states = dfs_attention(query, key, value, step_idx=self.step_idx,
+                                              **self._dfs_kwargs(S_q, S_k))
+            elif S_q == S_k and attention_mask is None:
+                hidden_states = full_attention(query, key, value, mode="flash", max_seqlen_q=S_q,
+                                               max_seqlen_kv=S_k, batch_size=query.shape[0])
+            else:  # cross-attention: different key length, not part of the DFS path
+                hidden_states = F.scaled_dot_product_attention(query, key, value)
 
         hidden_states = hidden_states.transpose(1, 2).flatten(2, 3).type_as(query)
         if hidden_states_img is not None:
             hidden_states = hidden_states + hidden_states_img
         hidden_states = attn.to_out[0](hidden_states)
         hidden_states = attn.to_out[1](hidden_states)
-
-        self.step_idx += 1
-        if self.step_idx == self.num_inference_steps * 2:
-            self.step_idx = 0
+        if not counted:
+            self._advance()
         return hidden_states

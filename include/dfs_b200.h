@@ -245,6 +245,22 @@ int dfs_block_sparse_fwd_ex(const void* q, const void* k, const void* v, const i
                             int out_token_major, int heads, int64_t seq_len, int64_t kv_len,
                             int head_dim, float scale, int32_t* status, void* stream);
 
+/* Several batch elements that share ONE set of block lists, in one launch: the two
+ * classifier-free-guidance passes of a Wan denoising step.  The reference runs them as two
+ * successive calls (its processor counts two calls per step, dfsattn/replace_wan.py:253,320-323,
+ * and its operator refuses batch > 1, dfsattn/attention_wan.py:219); the second call reuses the
+ * mask the first one cached, because the Wan cache key carries no step or sparsity term
+ * (attention_wan.py:147-154, :792-800).
+ *  q, k, v : bf16 [batch * H, L, D] (batch-major: element b holds heads b*H .. b*H+H-1).
+ *  idx/cnt : int32 [H, Qb, kmax] / [H, Qb]; head h of EVERY element uses list h.
+ *  out     : [batch, H, L, D] or, token-major, [batch, L, H*D].
+ * Everything else as dfs_block_sparse_fwd_ex; batch == 1 is the same call. */
+int dfs_block_sparse_fwd_batched(const void* q, const void* k, const void* v, const int32_t* idx,
+                                 const int32_t* cnt, int kmax, const int32_t* out_row_map, void* out,
+                                 int out_token_major, int batch, int heads, int64_t seq_len,
+                                 int64_t kv_len, int head_dim, float scale, int32_t* status,
+                                 void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -117,3 +117,32 @@ def test_sharded_entry_points_reject_bad_tables_before_any_launch():
                                             100, 100, 128, 0.1, None, None) == -1
     assert lib.dfs_block_sparse_fwd_sharded(0x1000, 0x1000, 0x1000, None, None, 0, None, tab.array, 2, 32, 32, 0,
                                             1, 100, 100, 128, 0.1, None, None) == -5
+
+
+def test_batched_attention_entry_point_rejects_bad_arguments_before_any_launch():
+    from dfsattn_b200 import _lib, ops
+    lib = _lib.lib
+    args = lambda batch, heads, q=0x1000: (q, 0x2000, 0x3000, None, None, 0, None, 0x4000, 0, batch, heads,
+                                           256, 256, 128, 0.1, None, None)
+    assert lib.dfs_block_sparse_fwd_batched(*args(0, 2)) == -3          # no batch element
+    assert lib.dfs_block_sparse_fwd_batched(*args(2, 0)) == -3          # no heads
+    assert lib.dfs_block_sparse_fwd_batched(*args(2, 40000)) == -3      # more grid rows than a launch has
+    assert lib.dfs_block_sparse_fwd_batched(*args(2, 2, q=None)) == -1  # null input
+    assert lib.dfs_block_sparse_fwd_batched(*args(2, 2, q=0x1008)) == -2
+    x = torch.zeros(3, 128, 128, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        ops.block_sparse_fwd(x, x, x, None, None, batch=2)              # CPU tensors; 3 is not 2 * heads
+
+
+def test_wan_processor_counts_a_batch_of_two_as_both_guidance_passes():
+    from dfsattn_b200.replace_wan import Wan_DFSAttn_Processor2_0 as WP
+    wp = WP("dfs", 0.3, 16, 128, None, 4, [0], 12, 12, 0.1, True, False)
+    wp.step_idx = 98
+    wp._advance(2)
+    assert wp.step_idx == 0                      # wraps at 100 like two single calls
+    wp.step_idx = 25
+    q = torch.zeros(2, 1, 128, 64)
+    with pytest.raises(ValueError):
+        wp._attend_self(q, q, q)                 # a pair cannot straddle two denoising steps
+    with pytest.raises(AssertionError):
+        wp._attend_self(torch.zeros(3, 1, 128, 64), q, q)

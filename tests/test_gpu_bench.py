@@ -35,6 +35,12 @@ def test_call_workload_line():
     assert "sm_mhz" in d["clocks"] and "reasons" in d["clocks"]
 
 
+def test_wan_workload_line_times_the_guidance_pair():
+    d = _run("--workload", "tiny_wan", "--steps", "3", "--warmup", "3", "--cpu-blocks", "4")
+    assert d["value"] > 0 and d["config"]["workload"] == "tiny_wan"
+    assert d["stages"]["cfg_two_calls_ms"] > 0 and d["stages"]["cfg_pair_call_ms"] > 0
+
+
 def test_trace_workload_line():
     d = _run("--workload", "tiny_trace", "--steps", "1", "--warmup", "1")
     assert d["value"] > 0 and d["config"]["denoising_steps"] == 50 and d["config"]["layers"] == 2
