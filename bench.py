@@ -531,9 +531,12 @@ def run_gpu(args, spec, rank, local_rank, world):
         def two_calls():
             wan_attention(q2[0:1], k2[0:1], v2[0:1], step_idx=26, **wkw)
             wan_attention(q2[1:2], k2[1:2], v2[1:2], step_idx=27, **wkw)
-        t_two = timed(two_calls, n_stage, barrier, warm=2) / n_stage
-        t_pair = timed(lambda: dfs_attention_cfg_pair(q2, k2, v2, step_idx=26, **wkw), n_stage, barrier,
-                       warm=2) / n_stage
+        pair_call = lambda: dfs_attention_cfg_pair(q2, k2, v2, step_idx=26, **wkw)  # noqa: E731
+        # alternate the two forms (the clocks settle during the first loops under the power cap); best of two
+        t_two = t_pair = float("inf")
+        for rnd in range(2):
+            t_two = min(t_two, timed(two_calls, n_stage, barrier, warm=2 - rnd) / n_stage)
+            t_pair = min(t_pair, timed(pair_call, n_stage, barrier, warm=2 - rnd) / n_stage)
         stages["cfg_two_calls_ms"] = 1e3 * reduce(t_two, dist.ReduceOp.MAX if world > 1 else None)
         stages["cfg_pair_call_ms"] = 1e3 * reduce(t_pair, dist.ReduceOp.MAX if world > 1 else None)
         del q2, k2, v2
