@@ -2,7 +2,7 @@
 
 Run in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 It imports ``dfsattn.attention_hyvideo`` / ``dfsattn.attention_wan`` from the
 reference checkout, feeds them seeded synthetic inputs and stores the results
@@ -66,7 +66,9 @@ def case_inputs(spec, seed=0):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit(f"usage: python {sys.argv[0]} <checkout of codesiena/DFSattn>")
+    ref_root = sys.argv[1]
     sys.path.insert(0, ref_root)
     import dfsattn.attention_hyvideo as ref_hy
     import dfsattn.attention_wan as ref_wan

@@ -1,6 +1,6 @@
 """Golden fixtures for the fused pre-attention step, from the REFERENCE's own Wan processor.
 
-    python tests/golden/make_golden_prepare.py [/path/to/reference]
+    python tests/golden/make_golden_prepare.py /path/to/reference
 
 The reference's ``Wan_DFSAttn_Processor2_0.__call__`` (``dfsattn/replace_wan.py:135-324``) is run
 on CPU in bf16 with mode="flash", which takes its PyTorch fallback for the RMSNorm and for the
@@ -32,7 +32,9 @@ def u16(t):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit(f"usage: python {sys.argv[0]} <checkout of codesiena/DFSattn>")
+    ref_root = sys.argv[1]
     sys.path.insert(0, ref_root)
     for name in ("diffusers", "diffusers.models", "diffusers.models.attention_processor"):
         sys.modules.setdefault(name, types.ModuleType(name))
