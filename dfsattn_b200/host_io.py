@@ -6,7 +6,9 @@ groups and the host->device copy of group g+1, the attention of group g and the
 device->host copy of group g-1 run concurrently on three CUDA streams (uploads are
 queued two groups ahead, into one device staging buffer allocated per call).  Each
 group keeps its own mask-cache entry (cache key ``(layer_idx, group)``), so the
-refresh / reuse schedule of the operator is unchanged.
+refresh / reuse schedule of the operator is unchanged.  The first three and the
+last two groups are single heads when there are enough heads: the first upload and
+the last download are the only copies nothing overlaps, so they are kept short.
 """
 from typing import Optional
 
@@ -15,9 +17,27 @@ import torch
 from . import attention_hyvideo, attention_wan
 
 
+def group_bounds(heads: int, groups: int, ramp: bool = True):
+    """[h0, h1) of each head group: ``groups`` near-equal groups, or, with ``ramp`` and at least 10
+    heads and 6 groups, three single heads first (a head is uploaded a little faster than it is
+    attended, so the uploads get ahead of the kernels while the groups are small), two single heads
+    last, and the rest split evenly in between."""
+    groups = max(1, min(int(groups), heads))
+    if ramp and heads >= 10 and groups >= 6:
+        inner, n = heads - 5, groups - 5
+        sizes = [1, 1, 1] + [(i + 1) * inner // n - i * inner // n for i in range(n)] + [1, 1]
+    else:
+        sizes = [(g + 1) * heads // groups - g * heads // groups for g in range(groups)]
+    bounds, h = [], 0
+    for sz in sizes:
+        bounds.append((h, h + sz))
+        h += sz
+    return bounds
+
+
 def dfs_attention_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None,
                        head_groups: int = 12, device="cuda", flavor: str = "hyvideo", layer_idx: int = 0,
-                       **kwargs) -> torch.Tensor:
+                       ramp: bool = True, **kwargs) -> torch.Tensor:
     """q, k, v: host tensors [1, H, L, D] (pinned memory makes the copies asynchronous).
     Returns the host tensor ``out`` ([1, H, L, D], pinned if allocated here).  ``kwargs`` are those of
     ``dfs_attention`` (step_idx, skip_steps, cache_interval, sparsity, ..., video_perm)."""
@@ -26,8 +46,8 @@ def dfs_attention_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: O
     fn = attention_hyvideo.dfs_attention if flavor == "hyvideo" else attention_wan.dfs_attention
     dev = torch.device(device)
     H = q.shape[1]
-    groups = max(1, min(head_groups, H))
-    bounds = [(g * H // groups, (g + 1) * H // groups) for g in range(groups)]
+    bounds = group_bounds(H, head_groups, ramp)
+    groups = len(bounds)
     if out is None:
         out = torch.empty(q.shape, dtype=q.dtype).pin_memory()
     compute = torch.cuda.current_stream(dev)

@@ -146,3 +146,15 @@ def test_wan_processor_counts_a_batch_of_two_as_both_guidance_passes():
         wp._attend_self(q, q, q)                 # a pair cannot straddle two denoising steps
     with pytest.raises(AssertionError):
         wp._attend_self(torch.zeros(3, 1, 128, 64), q, q)
+
+
+def test_host_entry_point_head_groups_cover_every_head_once():
+    from dfsattn_b200.host_io import group_bounds
+    for heads, groups in ((24, 12), (40, 12), (3, 12), (10, 6), (24, 4), (7, 7), (5, 1), (1, 1)):
+        for ramp in (True, False):
+            b = group_bounds(heads, groups, ramp)
+            assert b[0][0] == 0 and b[-1][1] == heads and len(b) == min(groups, heads)
+            assert all(x[1] == y[0] for x, y in zip(b, b[1:])) and all(h1 > h0 for h0, h1 in b)
+    sizes = [h1 - h0 for h0, h1 in group_bounds(24, 12)]
+    assert sizes[:3] == [1, 1, 1] and sizes[-2:] == [1, 1]      # short first upload, short last download
+    assert [h1 - h0 for h0, h1 in group_bounds(24, 12, ramp=False)] == [2] * 12

@@ -213,3 +213,11 @@ def test_host_buffer_entry_point_matches_device_call():
     assert torch.equal(got, want)       # heads are independent: grouping them changes nothing
     with pytest.raises(ValueError):
         dfs_attention_host(qh.cuda(), kh.cuda(), vh.cuda(), **kw)
+    # enough heads for the ramp (single heads at both ends, uneven groups in between)
+    q12, k12, v12 = (torch.cat([t, t.flip(2), t * 0.5, -t], 1).contiguous().pin_memory()
+                     for t in (qh, kh, vh))
+    assert q12.shape[1] == 12
+    want = dfs_attention(q12.cuda(), k12.cuda(), v12.cuda(), layer_idx=7, **kw).cpu()
+    got = dfs_attention_host(q12, k12, v12, head_groups=7, layer_idx=8, **kw)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
