@@ -193,6 +193,53 @@ def block_mask_wan(q, k, perm, sparsity, tile=16, block=128):
     return select_wan(sums, q.shape[2], sparsity, block)
 
 
+def fine_mask_hyvideo(q, k, perm, video_len, sparsity, fine_top_p, tile=16, block=128):
+    """The "kp" selector: bool mask [H, ceil(L/tile), ceil(L/tile)] over tile x tile token squares.
+
+    dfsattn/attention_hyvideo.py:481-489 and :211-302: the coarse top-k choice of video key blocks
+    is kept (forced text / boundary columns are not part of it); inside every chosen 128 x 128 pair
+    of the region before the first boundary block its 8 x 8 softmax-ed tile scores are ranked
+    jointly, largest first, and a tile stays while the scores ranked before it sum to less than
+    fine_top_p times the pair's total (:283-293); fine_top_p >= 1 keeps whole pairs (:266-281).
+    Columns from the boundary block on are on for every earlier row, and every row from the
+    boundary block on is fully on (:298-301) -- also when there is no text."""
+    if tile != 16 or block != 128:
+        raise ValueError("kp mode requires 128x128 coarse blocks and 16x16 sub-blocks")
+    b, h, L, d = q.shape
+    tpb = block // tile
+    ts = tile_score_hyvideo(q, k, perm, video_len, tile, block)
+    vb, kb = math.ceil(video_len / block), math.ceil(L / block)
+    sums = _block_sums(ts, vb, kb, tpb)
+    dense_start = video_len // block
+    n_text_blocks = max(0, kb - dense_start)
+    kk = max(1, int(sparsity * kb))
+    coarse = torch.zeros((h, vb, kb), dtype=torch.bool)
+    if n_text_blocks > 0:
+        if kk - n_text_blocks <= 0:
+            raise AssertionError("num_video_blocks_to_select must be non-negative")
+        top = torch.topk(sums[0, :, :, :dense_start], k=kk - n_text_blocks, dim=-1).indices
+    else:
+        top = torch.topk(sums[0], k=kk, dim=-1).indices
+    coarse.scatter_(-1, top, True)
+    nf = math.ceil(L / tile)
+    dfs = min(dense_start * tpb, nf)
+    fine = torch.zeros((h, nf, nf), dtype=torch.bool)
+    for hh in range(h):
+        for qb, cb in coarse[hh, :dense_start, :dense_start].nonzero().tolist():
+            vals = ts[0, hh, qb * tpb:(qb + 1) * tpb, cb * tpb:(cb + 1) * tpb].reshape(-1).float()
+            if fine_top_p >= 1.0:
+                keep = torch.ones_like(vals, dtype=torch.bool)
+            else:
+                order = torch.argsort(vals, descending=True)
+                ranked = vals[order]
+                keep = torch.zeros_like(vals, dtype=torch.bool)
+                keep[order] = (ranked.cumsum(0) - ranked) < ranked.sum() * fine_top_p
+            fine[hh, qb * tpb:(qb + 1) * tpb, cb * tpb:(cb + 1) * tpb] = keep.view(tpb, tpb)
+    fine[:, :dfs, dfs:] = True
+    fine[:, dfs:, :] = True
+    return fine
+
+
 def block_interaction_count(mask, seq_len, block=128):
     """Exact selected (q,k) token pairs; dfsattn/attention_hyvideo.py:521-546."""
     qb, kb = mask.shape[-2:]

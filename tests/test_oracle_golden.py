@@ -1,11 +1,12 @@
 """CPU: the oracle restatement against fixtures produced by the reference's own code."""
+import os
 import numpy as np
 import pytest
 import torch
 
 import oracle
 from oracle import dfs as odfs
-from golden_cases import CASES, ROW_STRIDE, checksum, inputs, load
+from golden_cases import CASES, GOLDEN, ROW_STRIDE, checksum, inputs, load
 
 
 def test_schedule_matches_reference_tables(golden_dir):
@@ -104,3 +105,18 @@ def test_varlen_second_segment_is_independent():
     second = torch.nn.functional.scaled_dot_product_attention(q[:, :, valid:], k[:, :, valid:], v[:, :, valid:])
     torch.testing.assert_close(o[:, :, :valid], first, atol=1e-5, rtol=1e-5)
     torch.testing.assert_close(o[:, :, valid:], second, atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("name", list(CASES))
+@pytest.mark.parametrize("tag,p", [("p90", 0.9), ("p50", 0.5)])
+def test_kp_fine_mask_matches_the_reference(name, tag, p):
+    """oracle.fine_mask_hyvideo against the masks the reference's own kp selector produced."""
+    g = np.load(os.path.join(GOLDEN, "kp_" + name + ".npz"))
+    shape = tuple(int(x) for x in g[f"fine_shape_{tag}"])
+    want = np.unpackbits(g[f"fine_bits_{tag}"])[: int(np.prod(shape))].reshape(shape).astype(bool)
+    spec = CASES[name]
+    q, k, v, vperm = inputs(name)
+    L = q.shape[2]
+    perm, _ = oracle.build_permutation(vperm, L, L - spec["text"])
+    got = oracle.fine_mask_hyvideo(q, k, perm, L - spec["text"], spec["sparsity"], p).numpy()
+    assert got.shape == shape and np.array_equal(got, want)
