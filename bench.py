@@ -506,6 +506,22 @@ def run_gpu(args, spec, rank, local_rank, world):
         "attention_ms": 1e3 * t_attn,
     }
 
+    if hy:
+        # The kp selector (fine top-p over the 16 x 16-token tiles inside the chosen blocks): what the tile
+        # maps cost at a refresh call and what the attention kernel takes with them (not part of `value`).
+        kp_lists = engine.compute_block_lists(qp, kp, video_len, spec["sparsity"], "hyvideo", fine_top_p=0.9)
+        t_kp = timed(lambda: engine.compute_block_lists(qp, kp, video_len, spec["sparsity"], "hyvideo",
+                                                        fine_top_p=0.9), n_stage, barrier, warm=1) / n_stage
+        t_kp_attn = timed(lambda: ops.block_sparse_fwd(qp, kp, vp, kp_lists.idx, kp_lists.cnt, out_row_map=perm,
+                                                       out=out_buf, fine=kp_lists.fine), n_stage, barrier,
+                          warm=1) / n_stage
+        stages["kp_score_select_refine_ms"] = 1e3 * t_kp
+        stages["kp_attention_ms"] = 1e3 * reduce(t_kp_attn, dist.ReduceOp.MAX if world > 1 else None)
+        bytes8 = kp_lists.fine.view(torch.uint8)
+        kept = sum(int(((bytes8 >> b) & 1).sum()) for b in range(8))
+        stages["kp_tiles_kept_frac"] = kept / (64.0 * int(kp_lists.cnt.sum()))
+        del kp_lists, bytes8
+
     # The processor-side fused step that makes the permute above unnecessary: projections
     # [L, H*D] -> normalised, rotated, permuted head-major Q/K/V in one pass (not part of `value`).
     src = [torch.randn(L, h_local * D, device=dev, dtype=torch.bfloat16) for _ in range(3)]

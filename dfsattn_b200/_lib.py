@@ -29,6 +29,8 @@ SIGNATURES = {
     "dfs_block_scores_static_max_bytes": (c_int64, []),
     "dfs_block_scores_static": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int,
                                         c_int, c_void_p, c_void_p, c_void_p]),
+    "dfs_fine_top_p": (c_int, [c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p,
+                               c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),
     "dfs_select_topk": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                 c_void_p, c_int, c_void_p, c_void_p]),
     "dfs_block_sparse_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
@@ -36,6 +38,9 @@ SIGNATURES = {
     "dfs_block_sparse_fwd_ex": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                         c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_float, c_void_p,
                                         c_void_p]),
+    "dfs_block_sparse_fwd_fine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                          c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_float,
+                                          c_void_p, c_void_p]),
     "dfs_block_sparse_fwd_batched": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                              c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int, c_float,
                                              c_void_p, c_void_p]),

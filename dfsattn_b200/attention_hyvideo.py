@@ -6,6 +6,9 @@ the native top-k path: ``_compute_cache_schedule`` (:40-65), ``DFS_Attention``
 :1492-1740) and ``dfs_attention`` (:1743-1982).  The PyTorch gathers, pooled
 scoring, ``torch.topk`` and the third-party block-sparse kernel are replaced by
 calls into libdfs_b200.so; masks are kept as device-resident index lists.
+``selector_mode="kp"`` (:481-489, :211-302: fine top-p over the 16 x 16-token
+tiles inside the chosen blocks) adds one 64-bit tile map per list entry, which
+the same attention kernel applies to its scores.
 Knobs of the reference's other backends are accepted and rejected with
 ``ValueError`` -- there is no dispatch and no fallback.
 """
@@ -29,11 +32,18 @@ def _compute_cache_schedule(step_idx: int, skip_steps: int, cache_interval: int,
     return ops.cache_schedule(step_idx, skip_steps, cache_interval, sparsity, sparsity_dcrt)
 
 
-def _reject_unsupported(sparse_execution, selector_mode, block_top_p, token_top_k, block_size, tile_size):
+def _reject_unsupported(sparse_execution, selector_mode, block_top_p, token_top_k, block_size, tile_size,
+                        fine_top_p=None, kp_allowed=False):
     if sparse_execution != "native":
         raise ValueError(f"sparse_execution={sparse_execution!r}: only 'native' is built for B200")
-    if selector_mode != "topk":
-        raise ValueError(f"selector_mode={selector_mode!r}: only 'topk' is built for B200")
+    if selector_mode == "kp" and kp_allowed:
+        if tile_size != 16 or block_size != 128:
+            raise ValueError("kp mode requires 128x128 coarse blocks and 16x16 sub-blocks")
+        if fine_top_p is None or not fine_top_p > 0:
+            raise ValueError("kp mode needs fine_top_p > 0")
+    elif selector_mode != "topk":
+        raise ValueError(f"selector_mode={selector_mode!r}: 'topk' (both operators) and 'kp' (HunyuanVideo "
+                         "operator) are built for B200")
     if block_top_p is not None:
         raise ValueError("block_top_p is not supported (top-k selection only)")
     if token_top_k:
@@ -93,7 +103,8 @@ class DFS_Attention(nn.Module):
         if self.q_tile_size != self.k_tile_size:
             raise ValueError("q_tile_size and k_tile_size must be equal")
         return engine.compute_block_lists(q_perm, k_perm, self._video_len(q_perm.shape[1]), sparse_ratio,
-                                          self.flavor, tile=self.q_tile_size)
+                                          self.flavor, tile=self.q_tile_size,
+                                          fine_top_p=self.fine_top_p if self.selector_mode == "kp" else None)
 
     def forward(self, q, k, v, attn_mask=None, causal: bool = False, drop_rate: float = 0.0,
                 cu_seqlens_q=None, cu_seqlens_kv=None, max_seqlen_q=None, max_seqlen_kv=None,
@@ -109,7 +120,7 @@ class DFS_Attention(nn.Module):
         assert batch_size == 1 and q.shape[0] == 1, \
             "DFS Attention with block sparse currently supports batch size 1."
         _reject_unsupported(self.sparse_execution, self.selector_mode, self.block_top_p, self.token_top_k,
-                            self.block_size, self.q_tile_size)
+                            self.block_size, self.q_tile_size, self.fine_top_p, kp_allowed=self.flavor == "hyvideo")
         out_dtype = q.dtype
         device = q.device
         seq_len = q.shape[2]
@@ -133,6 +144,11 @@ class DFS_Attention(nn.Module):
             rec.stop(t_topk, phase="topk_mask", step_idx=self.step_idx, layer_idx=self.layer_idx, device=device)
             mask_recomputed = True
             if self.cache_flag:
+                if self.selector_mode == "kp":
+                    # as the reference (:1166-1178): only the current schedule entry of a layer is kept
+                    for key in [kk for kk in cls._cached_metadata
+                                if kk[0] == self.layer_idx and kk != self._mask_cache_key()]:
+                        del cls._cached_metadata[key]
                 cls._cached_metadata[self._mask_cache_key()] = {"block_lists": lists}
             rec.stop(t_sel, phase="topk_routing", step_idx=self.step_idx, layer_idx=self.layer_idx,
                      device=device)
@@ -156,7 +172,14 @@ class DFS_Attention(nn.Module):
 
     def _record_density(self, lists: BlockLists, seq_len: int) -> None:
         cls = type(self)
-        pairs = ops.interaction_count(lists.idx, lists.cnt, lists.idx.shape[0], seq_len, self.block_size)
+        if lists.fine is not None:
+            # kp: density of the 16 x 16-token mask (the reference counts with logical_block_size 16, :1243)
+            fine = lists.to_fine_mask(seq_len)
+            size = torch.full((fine.shape[1],), 16.0, dtype=torch.float64, device=fine.device)
+            size[-1] = seq_len - 16 * (fine.shape[1] - 1)
+            pairs = int((fine.double() * size[None, :, None] * size[None, None, :]).sum().item())
+        else:
+            pairs = ops.interaction_count(lists.idx, lists.cnt, lists.idx.shape[0], seq_len, self.block_size)
         total = lists.idx.shape[0] * seq_len * seq_len
         cls.density_records.setdefault(self.step_idx, {})[self.layer_idx] = pairs / total
         cls.sparsity_records.setdefault(self.step_idx, {})[self.layer_idx] = {
@@ -254,7 +277,8 @@ def dfs_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, step_idx: i
     for name in unsupported:
         if not name.startswith("flashinfer64_"):
             raise TypeError(f"dfs_attention() got an unexpected keyword argument {name!r}")
-    _reject_unsupported(sparse_execution, selector_mode, block_top_p, token_top_k, block_size, tile_size)
+    _reject_unsupported(sparse_execution, selector_mode, block_top_p, token_top_k, block_size, tile_size,
+                        fine_top_p, kp_allowed=True)
     inst = _dfs_attention_instances.get(layer_idx)
     if inst is None:
         inst = DFS_Attention(step_idx, layer_idx, sparsity, cache_flag, video_len, video_perm, block_size,

@@ -76,6 +76,9 @@ struct SmemLayout {
 struct Params {
   const int32_t* idx;   // [H, Qb, kmax] or nullptr (all key blocks)
   const int32_t* cnt;   // [H, Qb]
+  // [H, Qb, kmax] or nullptr: per listed block a 64-bit map of its 16 x 16-token tiles, bit 8 * i + j =
+  // (query tile i, key tile j) is attended; read only by the kFine instantiation
+  const unsigned long long* fine;
   const int32_t* out_row_map;
   __nv_bfloat16* out;
   int32_t* status;
@@ -175,15 +178,21 @@ __device__ __forceinline__ void mask_tail(uint32_t (&r)[64], int valid, int t4) 
 // One pass over a thread's share of a score tile (two rows a and b): P = exp2(S*c - m*c) packed as
 // bf16 pairs (P column 4i + t of a row = keys 8i + 2t, 8i + 2t + 1), the tile's partial row sums,
 // and with kTrackMax the thread's share of the tile's raw row maxima.  The first kPoly groups take
-// their exponentials on the FMA pipe.
-template <int kPoly, bool kTrackMax>
+// their exponentials on the FMA pipe.  With kFine, key tile t (columns 16t .. 16t + 15: groups 2t and
+// 2t + 1) takes part only if bit t of `keep` is set; the 16 rows of a softmax warp are one query
+// tile, so the test is uniform over the warp and a dropped tile costs two stores of zero.
+template <int kPoly, bool kTrackMax, bool kFine>
 __device__ __forceinline__ void exp_pass(const uint32_t (&r)[64], uint64_t c2, uint64_t nma2, uint64_t nmb2,
                                          uint32_t (&packed)[32], uint64_t& ta0, uint64_t& ta1, uint64_t& tb0,
-                                         uint64_t& tb1, float& mt_a, float& mt_b) {
+                                         uint64_t& tb1, float& mt_a, float& mt_b, uint32_t keep) {
   float xa0 = -INFINITY, xa1 = -INFINITY, xb0 = -INFINITY, xb1 = -INFINITY;
   ta0 = ta1 = tb0 = tb1 = pack2(0.f, 0.f);
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
+    if (kFine && !((keep >> (i >> 1)) & 1u)) {
+      packed[2 * i] = packed[2 * i + 1] = 0u;
+      continue;
+    }
     const float sa0 = __uint_as_float(r[4 * i]), sa1 = __uint_as_float(r[4 * i + 1]);
     const float sb0 = __uint_as_float(r[4 * i + 2]), sb1 = __uint_as_float(r[4 * i + 3]);
     if (kTrackMax) {
@@ -236,7 +245,7 @@ __device__ __forceinline__ void exp_pass(const uint32_t (&r)[64], uint64_t c2, u
 #define DFS_POLY_GROUPS_D64 8
 #endif
 
-template <int HD>
+template <int HD, bool kFine>
 __global__ void __launch_bounds__(kThreads, 1)
     bsattn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const Params p) {
@@ -442,10 +451,20 @@ __global__ void __launch_bounds__(kThreads, 1)
     const bool dump = p.debug != nullptr && qb == 0 && head == 0 && n_tiles > 0;
     const uint32_t o_addr = tmem_base + lane_sel + kColO;
     int kb_next = n_tiles > 0 ? (my_idx ? __ldg(my_idx) : 0) : 0;
+    // tile map byte of this warp's query tile for the current and the next listed block
+    const unsigned long long* __restrict__ my_fine =
+        (kFine && p.fine != nullptr && my_idx != nullptr)
+            ? p.fine + (static_cast<size_t>(lhead) * p.q_blocks + qb) * p.kmax : nullptr;
+    const int fine_shift = 8 * (lane_base >> 4);
+    uint32_t keep_next = 0xffu;
+    if (kFine && my_fine != nullptr && n_tiles > 0) keep_next = static_cast<uint32_t>(__ldg(my_fine) >> fine_shift) & 0xffu;
 
     for (int j = 0; j < n_tiles; ++j) {
       const int kb = kb_next;
       if (j + 1 < n_tiles) kb_next = my_idx ? __ldg(my_idx + j + 1) : j + 1;
+      const uint32_t keep = keep_next;
+      if (kFine && my_fine != nullptr && j + 1 < n_tiles)
+        keep_next = static_cast<uint32_t>(__ldg(my_fine + j + 1) >> fine_shift) & 0xffu;
       // keys past kv_len (partial last block, zero-filled by TMA) are masked
       const long long key0 = static_cast<long long>(kb) * kBlockN;
       const int valid = key0 + kBlockN > p.kv_len ? static_cast<int>(p.kv_len - key0) : kBlockN;
@@ -455,6 +474,18 @@ __global__ void __launch_bounds__(kThreads, 1)
 
       const uint32_t s_addr = tmem_base + lane_sel + s_col(j);
       const uint32_t p_addr = s_addr;  // P goes over the first half of the scores it came from
+      if (kFine && keep == 0u) {
+        // no key tile of this block is kept for this warp's query tile: P = 0, nothing else to do
+        uint32_t zeros[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) zeros[i] = 0u;
+        tmem_st_16x128b_x16(p_addr, zeros);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[j % kSBufs]);
+        continue;
+      }
       uint32_t r[64];
       tmem_ld_16x256b_x16(s_addr, r);
       tmem_wait_ld();
@@ -480,12 +511,17 @@ __global__ void __launch_bounds__(kThreads, 1)
       float mt_a = -INFINITY, mt_b = -INFINITY;
       bool redo = true;  // the exp2 pass against the final reference is still to be done
       if (kSpeculate && j > 0) {
-        const float nma = -m_a * c, nmb = -m_b * c;  // finite: every row saw a key in the first tile
-        exp_pass<kPolyGroups, true>(r, c2, pack2(nma, nma), pack2(nmb, nmb), packed, ta0, ta1, tb0, tb1, mt_a, mt_b);
+        // finite without tile maps: every row saw a key in the first tile; with them a row may still
+        // be without a reference (-inf), which the redo below then settles
+        const float nma = (kFine && m_a == -INFINITY) ? 0.f : -m_a * c;
+        const float nmb = (kFine && m_b == -INFINITY) ? 0.f : -m_b * c;
+        exp_pass<kPolyGroups, true, kFine>(r, c2, pack2(nma, nma), pack2(nmb, nmb), packed, ta0, ta1, tb0, tb1, mt_a,
+                                           mt_b, keep);
       } else {
         float xa0 = -INFINITY, xa1 = -INFINITY, xb0 = -INFINITY, xb1 = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {
+          if (kFine && !((keep >> (i >> 1)) & 1u)) continue;  // a dropped key tile
           xa0 = max3(xa0, __uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]));
           xb0 = max3(xb0, __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
           xa1 = max3(xa1, __uint_as_float(r[4 * i + 4]), __uint_as_float(r[4 * i + 5]));
@@ -549,8 +585,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         // a row whose keys are all masked keeps the reference -inf: its exponentials are exp2(-inf) = 0
         const float nma = (m_a == -INFINITY) ? 0.f : -m_a * c, nmb = (m_b == -INFINITY) ? 0.f : -m_b * c;
         float unused_a, unused_b;
-        exp_pass<kPolyGroups, false>(r, c2, pack2(nma, nma), pack2(nmb, nmb), packed, ta0, ta1, tb0, tb1, unused_a,
-                                     unused_b);
+        exp_pass<kPolyGroups, false, kFine>(r, c2, pack2(nma, nma), pack2(nmb, nmb), packed, ta0, ta1, tb0, tb1,
+                                            unused_a, unused_b, keep);
       }
       // only now: the scores are not needed any more
       tmem_st_16x128b_x16(p_addr, packed);
@@ -578,7 +614,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       ok = mbar_wait_bounded(&v_empty[(n_tiles - 1) % kStages], ((n_tiles - 1) / kStages) & 1, abort_flag);
     if (ok) {
       tc_fence_after_sync();
-      const float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+      // a row that never saw an unmasked key still has no reference maximum; its sum is not exactly
+      // zero (masked scores on the polynomial exp2 come out as 2^-126), its result is
+      const float inv_a = (l_a > 0.f && m_a != -INFINITY) ? 1.0f / l_a : 0.f;
+      const float inv_b = (l_b > 0.f && m_b != -INFINITY) ? 1.0f / l_b : 0.f;
       const long long tok_a = static_cast<long long>(qb) * kBlockM + row_a, tok_b = tok_a + 8;
       const bool live_a = tok_a < p.seq_len, live_b = tok_b < p.seq_len;  // a row with an empty list gets zeros
       long long dst_a = tok_a, dst_b = tok_b;
@@ -654,14 +693,14 @@ int make_tile_map(CUtensorMap* map, const void* base, int heads, int64_t seq_len
   return dfs_make_bf16_tile_map(map, base, heads, seq_len, head_dim);
 }
 
-template <int HD>
+template <int HD, bool kFine>
 int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int heads,
                cudaStream_t stream) {
   using L = SmemLayout<HD>;
-  DFS_CUDA_CHECK(cudaFuncSetAttribute(bsattn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  DFS_CUDA_CHECK(cudaFuncSetAttribute(bsattn_fwd_kernel<HD, kFine>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       L::kTotal));
   dim3 grid(p.q_blocks, heads);
-  bsattn_fwd_kernel<HD><<<grid, kThreads, L::kTotal, stream>>>(mq, mk, mv, p);
+  bsattn_fwd_kernel<HD, kFine><<<grid, kThreads, L::kTotal, stream>>>(mq, mk, mv, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -681,7 +720,7 @@ struct ShardedOut {
 };
 
 int block_sparse_fwd_impl(const void* q, const void* k, const void* v, const int32_t* idx, const int32_t* cnt,
-                          int kmax, const int32_t* out_row_map, void* out, int out_token_major,
+                          const uint64_t* fine, int kmax, const int32_t* out_row_map, void* out, int out_token_major,
                           const ShardedOut& sh, int batch, int heads, int64_t seq_len, int64_t kv_len,
                           int head_dim, float scale, int32_t* status, void* stream_) {
   // `heads` = heads of one batch element (what the lists cover); the tensors hold batch * heads heads
@@ -700,6 +739,8 @@ int block_sparse_fwd_impl(const void* q, const void* k, const void* v, const int
   }
   if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return DFS_ERR_NULL;
   if ((idx == nullptr) != (cnt == nullptr)) return DFS_ERR_NULL;
+  if (fine != nullptr && idx == nullptr) return DFS_ERR_NULL;  // tile maps belong to list entries
+  if ((reinterpret_cast<uintptr_t>(fine) & 7u) != 0) return DFS_ERR_ALIGN;
   if (!dfs_aligned16(q) || !dfs_aligned16(k) || !dfs_aligned16(v) || !dfs_aligned16(out)) return DFS_ERR_ALIGN;
   if (head_dim != 64 && head_dim != 128) return DFS_ERR_SHAPE;
   if (seq_len <= 0) return DFS_ERR_SHAPE;
@@ -717,6 +758,7 @@ int block_sparse_fwd_impl(const void* q, const void* k, const void* v, const int
   Params p;
   p.idx = idx;
   p.cnt = cnt;
+  p.fine = reinterpret_cast<const unsigned long long*>(fine);
   p.out_row_map = out_row_map;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.status = status;
@@ -737,8 +779,11 @@ int block_sparse_fwd_impl(const void* q, const void* k, const void* v, const int
   p.q_blocks = static_cast<int>((seq_len + kBlockM - 1) / kBlockM);
   p.k_blocks = static_cast<int>((kv_len + kBlockN - 1) / kBlockN);
   p.scale_log2 = scale * 1.4426950408889634f;
-  return head_dim == 128 ? launch_fwd<128>(mq, mk, mv, p, all_heads, stream)
-                         : launch_fwd<64>(mq, mk, mv, p, all_heads, stream);
+  if (fine != nullptr)
+    return head_dim == 128 ? launch_fwd<128, true>(mq, mk, mv, p, all_heads, stream)
+                           : launch_fwd<64, true>(mq, mk, mv, p, all_heads, stream);
+  return head_dim == 128 ? launch_fwd<128, false>(mq, mk, mv, p, all_heads, stream)
+                         : launch_fwd<64, false>(mq, mk, mv, p, all_heads, stream);
 }
 }  // namespace
 
@@ -746,7 +791,7 @@ extern "C" int dfs_block_sparse_fwd_ex(const void* q, const void* k, const void*
                                        const int32_t* cnt, int kmax, const int32_t* out_row_map, void* out,
                                        int out_token_major, int heads, int64_t seq_len, int64_t kv_len,
                                        int head_dim, float scale, int32_t* status, void* stream) {
-  return block_sparse_fwd_impl(q, k, v, idx, cnt, kmax, out_row_map, out, out_token_major, ShardedOut(), 1, heads,
+  return block_sparse_fwd_impl(q, k, v, idx, cnt, nullptr, kmax, out_row_map, out, out_token_major, ShardedOut(), 1, heads,
                                seq_len, kv_len, head_dim, scale, status, stream);
 }
 
@@ -755,8 +800,18 @@ extern "C" int dfs_block_sparse_fwd_batched(const void* q, const void* k, const 
                                             int out_token_major, int batch, int heads, int64_t seq_len,
                                             int64_t kv_len, int head_dim, float scale, int32_t* status,
                                             void* stream) {
-  return block_sparse_fwd_impl(q, k, v, idx, cnt, kmax, out_row_map, out, out_token_major, ShardedOut(), batch,
+  return block_sparse_fwd_impl(q, k, v, idx, cnt, nullptr, kmax, out_row_map, out, out_token_major, ShardedOut(), batch,
                                heads, seq_len, kv_len, head_dim, scale, status, stream);
+}
+
+extern "C" int dfs_block_sparse_fwd_fine(const void* q, const void* k, const void* v, const int32_t* idx,
+                                         const int32_t* cnt, const uint64_t* fine_bits, int kmax,
+                                         const int32_t* out_row_map, void* out, int out_token_major, int heads,
+                                         int64_t seq_len, int64_t kv_len, int head_dim, float scale,
+                                         int32_t* status, void* stream) {
+  if (fine_bits == nullptr) return DFS_ERR_NULL;
+  return block_sparse_fwd_impl(q, k, v, idx, cnt, fine_bits, kmax, out_row_map, out, out_token_major, ShardedOut(),
+                               1, heads, seq_len, kv_len, head_dim, scale, status, stream);
 }
 
 extern "C" int dfs_block_sparse_fwd_sharded(const void* q, const void* k, const void* v, const int32_t* idx,
@@ -772,7 +827,7 @@ extern "C" int dfs_block_sparse_fwd_sharded(const void* q, const void* k, const 
   sh.shard_rows = shard_rows;
   sh.shard_stride_rows = shard_stride_rows;
   sh.head0 = head0;
-  return block_sparse_fwd_impl(q, k, v, idx, cnt, kmax, out_row_map, nullptr, 0, sh, 1, heads, seq_len, kv_len,
+  return block_sparse_fwd_impl(q, k, v, idx, cnt, nullptr, kmax, out_row_map, nullptr, 0, sh, 1, heads, seq_len, kv_len,
                                head_dim, scale, status, stream);
 }
 

@@ -490,6 +490,178 @@ extern "C" int dfs_block_scores(const void* q_perm, const void* k_perm, int dtyp
 }
 
 // --------------------------------------------------------------------------
+// Fine top-p inside the chosen block pairs ("kp" selector)
+//
+// For every listed (query block, key block) pair of the refinable region the 8 x 8 softmax-ed
+// tile scores are recomputed from the pooled means and the stored log-sum-exps that the block
+// scoring left in its scratch, ranked jointly (larger first), and a tile is kept while the scores ranked
+// before it sum to less than top_p times the pair's total.  Result: one 64-bit map per list
+// entry, bit 8 * (query tile) + (key tile).  One CTA per (query block, head), one warp per pair.
+// --------------------------------------------------------------------------
+namespace {
+
+constexpr int kFineWarps = 8;
+
+template <int HD>
+__global__ void __launch_bounds__(kFineWarps * 32)
+fine_top_p_kernel(const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __restrict__ km,
+                  const float* __restrict__ lse, const int32_t* __restrict__ idx, const int32_t* __restrict__ cnt,
+                  unsigned long long* __restrict__ bits, ScoreShape s, int q_rows, int kmax, int n_rank,
+                  int dense_row_start, float top_p, float scale_log2) {
+  constexpr int kPad = HD + 4;  // fp32 row pitch in shared memory (rows start 4 banks apart)
+  __shared__ __align__(16) float q_s[8][kPad];
+  __shared__ __align__(16) float k_s[kFineWarps][8][kPad];
+  __shared__ float row_lse[8];
+  const int head = blockIdx.y, qb = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t list_at = (static_cast<size_t>(head) * q_rows + qb) * kmax;
+  const int n_list = cnt[static_cast<size_t>(head) * q_rows + qb];
+  const bool dense_row = qb >= dense_row_start || qb >= s.q_blocks;
+  if (dense_row) {  // rows from the first boundary block on keep whole blocks
+    for (int slot = threadIdx.x; slot < kmax; slot += blockDim.x) bits[list_at + slot] = slot < n_list ? ~0ull : 0ull;
+    return;
+  }
+  // normaliser of each of the 8 pooled query rows over ALL key tiles: log2 sum_c 2^lse[i][c]
+  {
+    const float* __restrict__ r = lse + (static_cast<size_t>(head) * s.nq + qb * 8 + warp) * s.k_blocks;
+    float m = -INFINITY;
+    for (int c = lane; c < s.k_blocks; c += 32) m = fmaxf(m, r[c]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float z = 0.f;
+    for (int c = lane; c < s.k_blocks; c += 32) z += exp2f(r[c] - m);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
+    if (lane == 0) row_lse[warp] = m + log2f(z);
+  }
+  // pooled query rows of this block as fp32 (hi + lo)
+  {
+    const __nv_bfloat16* __restrict__ hi = qm + (static_cast<size_t>(2 * head) * s.nq_pad + qb * 8) * HD;
+    const __nv_bfloat16* __restrict__ lo = hi + static_cast<size_t>(s.nq_pad) * HD;
+    for (int e = threadIdx.x; e < 8 * HD; e += blockDim.x)
+      q_s[e / HD][e % HD] = __bfloat162float(hi[e]) + __bfloat162float(lo[e]);
+  }
+  __syncthreads();
+
+  const int qi = lane >> 2, kj0 = (lane & 3) * 2;  // this lane's two tiles: (qi, kj0) and (qi, kj0 + 1)
+  const float my_lse = row_lse[qi];
+  for (int slot = warp; slot < kmax; slot += kFineWarps) {
+    if (slot >= n_list) {
+      if (lane == 0) bits[list_at + slot] = 0ull;
+      continue;
+    }
+    const int kb = idx[list_at + slot];
+    if (kb >= n_rank) {  // forced (text / boundary) key blocks stay whole
+      if (lane == 0) bits[list_at + slot] = ~0ull;
+      continue;
+    }
+    // stage the 8 pooled key rows of the block as fp32
+    const __nv_bfloat16* __restrict__ hi = km + (static_cast<size_t>(2 * head) * s.nk_pad + kb * 8) * HD;
+    const __nv_bfloat16* __restrict__ lo = hi + static_cast<size_t>(s.nk_pad) * HD;
+    __syncwarp();
+    for (int e = lane * 4; e < 8 * HD; e += 32 * 4) {  // consecutive lanes, consecutive 16-byte stores
+      const uint2 h4 = __ldg(reinterpret_cast<const uint2*>(hi + e));
+      const uint2 l4 = __ldg(reinterpret_cast<const uint2*>(lo + e));
+      float4 f;
+      f.x = __uint_as_float(h4.x << 16) + __uint_as_float(l4.x << 16);
+      f.y = __uint_as_float(h4.x & 0xffff0000u) + __uint_as_float(l4.x & 0xffff0000u);
+      f.z = __uint_as_float(h4.y << 16) + __uint_as_float(l4.y << 16);
+      f.w = __uint_as_float(h4.y & 0xffff0000u) + __uint_as_float(l4.y & 0xffff0000u);
+      *reinterpret_cast<float4*>(&k_s[warp][e / HD][e % HD]) = f;
+    }
+    __syncwarp();
+    float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;  // four independent partial sums per logit
+#pragma unroll 8
+    for (int c = 0; c < HD; c += 4) {
+      const float4 qv = *reinterpret_cast<const float4*>(&q_s[qi][c]);
+      const float4 a = *reinterpret_cast<const float4*>(&k_s[warp][kj0][c]);
+      const float4 b = *reinterpret_cast<const float4*>(&k_s[warp][kj0 + 1][c]);
+      s0.x = fmaf(qv.x, a.x, s0.x); s0.y = fmaf(qv.y, a.y, s0.y); s0.z = fmaf(qv.z, a.z, s0.z); s0.w = fmaf(qv.w, a.w, s0.w);
+      s1.x = fmaf(qv.x, b.x, s1.x); s1.y = fmaf(qv.y, b.y, s1.y); s1.z = fmaf(qv.z, b.z, s1.z); s1.w = fmaf(qv.w, b.w, s1.w);
+    }
+    const float d0 = (s0.x + s0.y) + (s0.z + s0.w), d1 = (s1.x + s1.y) + (s1.z + s1.w);
+    const float v0 = exp2f(fmaf(d0, scale_log2, -my_lse)), v1 = exp2f(fmaf(d1, scale_log2, -my_lse));
+    // Rank the 64 scores, largest first, with a bitonic sort over the warp (two per lane).  Key: the
+    // score's bits (non-negative floats order like their bit patterns) above 63 - tile index, so equal
+    // scores rank by index and every key is distinct.
+    unsigned long long k0 = (static_cast<unsigned long long>(__float_as_uint(v0)) << 32) | static_cast<unsigned>(63 - 2 * lane);
+    unsigned long long k1 = (static_cast<unsigned long long>(__float_as_uint(v1)) << 32) | static_cast<unsigned>(62 - 2 * lane);
+#pragma unroll
+    for (int k = 2; k <= 64; k <<= 1) {
+      const bool desc = ((2 * lane) & k) == 0;  // direction of this element's block in this round
+#pragma unroll
+      for (int j = k >> 1; j > 0; j >>= 1) {
+        if (j == 1) {  // the partner is the lane's other element
+          const bool swap = desc ? (k0 < k1) : (k0 > k1);
+          const unsigned long long lo_key = swap ? k1 : k0, hi_key = swap ? k0 : k1;
+          k0 = lo_key;
+          k1 = hi_key;
+        } else {
+          const unsigned long long o0 = __shfl_xor_sync(0xffffffffu, k0, j >> 1);
+          const unsigned long long o1 = __shfl_xor_sync(0xffffffffu, k1, j >> 1);
+          const bool take_max = (((lane & (j >> 1)) == 0) == desc);
+          k0 = take_max ? (k0 > o0 ? k0 : o0) : (k0 < o0 ? k0 : o0);
+          k1 = take_max ? (k1 > o1 ? k1 : o1) : (k1 < o1 ? k1 : o1);
+        }
+      }
+    }
+    // rank 2 * lane holds k0, rank 2 * lane + 1 holds k1: mass ranked before each of them
+    const float a = __uint_as_float(static_cast<uint32_t>(k0 >> 32)), b = __uint_as_float(static_cast<uint32_t>(k1 >> 32));
+    float inc = a + b;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += up;
+    }
+    const float before0 = inc - (a + b), before1 = before0 + a;
+    const float limit = __shfl_sync(0xffffffffu, inc, 31) * top_p;
+    const int i0 = 63 - static_cast<int>(k0 & 63ull), i1 = 63 - static_cast<int>(k1 & 63ull);
+    uint32_t lo_bits = 0u, hi_bits = 0u;
+    if (before0 < limit) (i0 < 32 ? lo_bits : hi_bits) |= 1u << (i0 & 31);
+    if (before1 < limit) (i1 < 32 ? lo_bits : hi_bits) |= 1u << (i1 & 31);
+    const uint32_t word = __reduce_or_sync(0xffffffffu, lo_bits);
+    const uint32_t hi_word = __reduce_or_sync(0xffffffffu, hi_bits);
+    if (lane == 0) bits[list_at + slot] = (static_cast<unsigned long long>(hi_word) << 32) | word;
+  }
+}
+
+}  // namespace
+
+extern "C" int dfs_fine_top_p(const void* workspace, int64_t workspace_bytes, int heads, int64_t seq_len,
+                              int64_t video_len, int head_dim, int tile, int block, int wan_layout,
+                              const int32_t* idx, const int32_t* cnt, int kmax, int q_rows, int n_rank,
+                              int dense_row_start, float fine_top_p, uint64_t* fine_bits, void* stream_) {
+  if (workspace == nullptr || idx == nullptr || cnt == nullptr || fine_bits == nullptr) return DFS_ERR_NULL;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0 || (reinterpret_cast<uintptr_t>(fine_bits) & 7u) != 0)
+    return DFS_ERR_ALIGN;
+  const int rc = check_shape(heads, seq_len, video_len, head_dim, tile, block, wan_layout);
+  if (rc != 0) return rc;
+  if (tile != 16) return DFS_ERR_SHAPE;  // the maps are 8 x 8: 16-token tiles inside 128-token blocks
+  const ScoreShape s = make_shape(heads, seq_len, video_len, head_dim, tile, wan_layout);
+  const Workspace w = make_workspace(s);
+  if (workspace_bytes < static_cast<int64_t>(w.total)) return DFS_ERR_WORKSPACE;
+  if (kmax <= 0 || q_rows < s.q_blocks || q_rows > s.k_blocks || n_rank < 0 || n_rank > s.k_blocks ||
+      dense_row_start < 0)
+    return DFS_ERR_RANGE;
+  if (!(fine_top_p > 0.f)) return DFS_ERR_RANGE;
+  const char* base = static_cast<const char*>(workspace);
+  const __nv_bfloat16* qm = reinterpret_cast<const __nv_bfloat16*>(base + w.qm_off);
+  const __nv_bfloat16* km = reinterpret_cast<const __nv_bfloat16*>(base + w.km_off);
+  const float* lse = reinterpret_cast<const float*>(base + w.lse_off);
+  const float scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(head_dim));
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  dim3 grid(q_rows, heads);
+  auto* out = reinterpret_cast<unsigned long long*>(fine_bits);
+  if (head_dim == 128)
+    fine_top_p_kernel<128><<<grid, kFineWarps * 32, 0, stream>>>(qm, km, lse, idx, cnt, out, s, q_rows, kmax, n_rank,
+                                                                 dense_row_start, fine_top_p, scale_log2);
+  else
+    fine_top_p_kernel<64><<<grid, kFineWarps * 32, 0, stream>>>(qm, km, lse, idx, cnt, out, s, q_rows, kmax, n_rank,
+                                                                dense_row_start, fine_top_p, scale_log2);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// --------------------------------------------------------------------------
 // Scoring without any allocation by the caller or by the library.
 //
 // Some hosts of this library may not allocate device memory at the moment

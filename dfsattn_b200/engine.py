@@ -23,9 +23,30 @@ class BlockLists:
     idx: torch.Tensor  # int32 [H, Qb, kmax], -1 padded
     cnt: torch.Tensor  # int32 [H, Qb]
     k_blocks: int
+    # "kp" selector only: int64 [H, Qb, kmax], per list entry the 8 x 8 map of attended 16 x 16-token
+    # tiles (bit 8 * query tile + key tile); None = whole blocks
+    fine: Optional[torch.Tensor] = None
 
     def clone(self) -> "BlockLists":
-        return BlockLists(self.idx.clone(), self.cnt.clone(), self.k_blocks)
+        return BlockLists(self.idx.clone(), self.cnt.clone(), self.k_blocks,
+                          None if self.fine is None else self.fine.clone())
+
+    def to_fine_mask(self, seq_len: int) -> torch.Tensor:
+        """bool [H, ceil(L/16), ceil(L/16)]: the reference's fine mask format
+        (dfsattn/attention_hyvideo.py:236-241), for inspection and tests."""
+        H, Qb, kmax = self.idx.shape
+        if self.fine is None:
+            full = self.to_bool_mask().repeat_interleave(8, 1).repeat_interleave(8, 2)
+        else:
+            shifts = torch.arange(64, device=self.idx.device, dtype=torch.int64)
+            tiles = ((self.fine[..., None] >> shifts) & 1).bool().view(H, Qb, kmax, 8, 8)
+            tiles = tiles & (self.idx >= 0)[..., None, None]
+            dense = torch.zeros((H, Qb, self.k_blocks + 1, 8, 8), dtype=torch.bool, device=self.idx.device)
+            safe = torch.where(self.idx >= 0, self.idx, torch.full_like(self.idx, self.k_blocks)).long()
+            dense.scatter_(2, safe[..., None, None].expand(-1, -1, -1, 8, 8), tiles)
+            full = dense[:, :, : self.k_blocks].permute(0, 1, 3, 2, 4).reshape(H, Qb * 8, self.k_blocks * 8)
+        nf = math.ceil(seq_len / 16)
+        return full[:, :nf, :nf]
 
     def to_bool_mask(self) -> torch.Tensor:
         """bool [H, Qb, Kb] (the reference's mask format)."""
@@ -104,7 +125,7 @@ def topk_block_num(sparsity: float, k_blocks: int) -> int:
 
 
 def select_lists(scores: torch.Tensor, seq_len: int, video_len: int, sparsity: float,
-                 flavor: str, want_mask: bool = False):
+                 flavor: str, want_mask: bool = False, kp: bool = False):
     """Index lists from fp32 block scores with the reference's budget rules.
 
     flavor "hyvideo": dfsattn/attention_hyvideo.py:424-443,491-501 (text and
@@ -127,23 +148,35 @@ def select_lists(scores: torch.Tensor, seq_len: int, video_len: int, sparsity: f
         n_rank = dense_start
     else:
         n_sel, n_rank = kk, kb
-    dense_row_start = dense_start if text_len > 0 else kb
+    # the kp selector keeps every row from the boundary block on dense, text or not (:298-301)
+    dense_row_start = dense_start if (text_len > 0 or (kp and n_text_blocks > 0)) else kb
     return ops.select_topk(scores, q_rows=kb, n_rank=n_rank, k_select=n_sel,
                            dense_row_start=dense_row_start, want_mask=want_mask)
 
 
 def compute_block_lists(q_perm, k_perm, video_len: int, sparsity: float, flavor: str,
-                        tile: int = ops.TILE) -> BlockLists:
-    """Scores + selection on permuted [H, L, D] tensors -> BlockLists."""
+                        tile: int = ops.TILE, fine_top_p: Optional[float] = None) -> BlockLists:
+    """Scores + selection on permuted [H, L, D] tensors -> BlockLists.  With ``fine_top_p`` (the
+    "kp" selector, HunyuanVideo flavour, 16-token tiles) the lists also carry the tile maps of
+    ``ops.fine_top_p``; a value >= 1 keeps whole blocks, as the reference does
+    (dfsattn/attention_hyvideo.py:266-281)."""
     H, L, D = q_perm.shape
     wan = flavor == "wan"
+    kp = fine_top_p is not None
+    if kp and (wan or tile != 16):
+        raise ValueError("kp mode requires the HunyuanVideo operator, 128x128 coarse blocks and 16x16 sub-blocks")
     need = ops.lib.dfs_score_workspace_bytes(H, L, L if wan else video_len, D, tile, BLOCK, int(wan))
     if need < 0:
         ops.check(int(need), "dfs_score_workspace_bytes")
-    scores = ops.block_scores(q_perm, k_perm, L if wan else video_len, wan, tile=tile,
-                              workspace=_workspace(q_perm.device, int(need)))
-    idx, cnt, _ = select_lists(scores, L, L if wan else video_len, sparsity, flavor)
-    return BlockLists(idx, cnt, math.ceil(L / BLOCK))
+    ws = _workspace(q_perm.device, int(need))
+    scores = ops.block_scores(q_perm, k_perm, L if wan else video_len, wan, tile=tile, workspace=ws)
+    idx, cnt, _ = select_lists(scores, L, L if wan else video_len, sparsity, flavor, kp=kp)
+    fine = None
+    if kp and fine_top_p < 1.0:
+        dense_start = video_len // BLOCK
+        fine = ops.fine_top_p(ws, H, L, video_len, D, False, idx, cnt, n_rank=dense_start,
+                              dense_row_start=dense_start, top_p=fine_top_p, tile=tile)
+    return BlockLists(idx, cnt, math.ceil(L / BLOCK), fine)
 
 
 def _as_heads(x: torch.Tensor) -> torch.Tensor:
@@ -191,6 +224,9 @@ def run_attention(qp, kp, vp, lists: Optional[BlockLists], perm_i32, valid_len: 
     H, L, D = qp.shape
     idx = lists.idx if lists is not None else None
     cnt = lists.cnt if lists is not None else None
+    fine = lists.fine if lists is not None else None
+    if fine is not None and (out_shards is not None or valid_len < L):
+        raise ValueError("tile maps (kp selector) are not combined with sharded output or a padded tail")
     if out_shards is not None:
         # the result is scattered to sequence shards on several GPUs (ops.ShardTable); no local copy
         if valid_len < L:
@@ -198,7 +234,7 @@ def run_attention(qp, kp, vp, lists: Optional[BlockLists], perm_i32, valid_len: 
         return ops.block_sparse_fwd(qp, kp, vp, idx, cnt, out_row_map=perm_i32, kv_len=valid_len,
                                     out_shards=out_shards, out_head0=out_head0)
     out = ops.block_sparse_fwd(qp, kp, vp, idx, cnt, out_row_map=perm_i32, kv_len=valid_len,
-                               token_major=token_major)
+                               token_major=token_major, fine=fine)
     if valid_len < L:
         tail = L - valid_len
         if perm_i32 is not None and not bool((perm_i32[valid_len:] == torch.arange(

@@ -139,6 +139,26 @@ def block_scores(q_perm, k_perm, video_len: int, wan_layout: bool, tile=TILE, bl
     return out
 
 
+def fine_top_p(workspace: torch.Tensor, heads: int, seq_len: int, video_len: int, head_dim: int,
+               wan_layout: bool, idx: torch.Tensor, cnt: torch.Tensor, n_rank: int, dense_row_start: int,
+               top_p: float, tile=TILE, block=BLOCK) -> torch.Tensor:
+    """64-bit tile maps int64 [H, Qb, kmax] for the lists (``dfs_fine_top_p``): which 16 x 16-token
+    tiles of each listed 128 x 128 pair are attended.  ``workspace`` is the scratch ``block_scores``
+    has just filled for the same shape."""
+    _need_cuda(workspace, idx, cnt)
+    if idx.dtype != torch.int32 or cnt.dtype != torch.int32 or not (idx.is_contiguous() and cnt.is_contiguous()):
+        raise ValueError("idx, cnt must be contiguous int32")
+    H, q_rows, kmax = idx.shape
+    if H != heads or tuple(cnt.shape) != (H, q_rows):
+        raise ValueError("lists do not match the head count")
+    bits = torch.empty((H, q_rows, kmax), dtype=torch.int64, device=idx.device)
+    check(lib.dfs_fine_top_p(workspace.data_ptr(), workspace.numel() * workspace.element_size(), heads, seq_len,
+                             video_len, head_dim, tile, block, int(wan_layout), idx.data_ptr(), cnt.data_ptr(),
+                             kmax, q_rows, int(n_rank), int(dense_row_start), float(top_p), bits.data_ptr(),
+                             _stream(idx.device)), "dfs_fine_top_p")
+    return bits
+
+
 def block_scores_static(q_perm, k_perm, video_len: int, wan_layout: bool, out: torch.Tensor,
                         tile=TILE, block=BLOCK) -> torch.Tensor:
     """Block scores into the caller's ``out`` [H, Rb, Kb] fp32 without allocating
@@ -209,14 +229,15 @@ def permute_qkv_sharded(q_tab: ShardTable, k_tab: ShardTable, v_tab: ShardTable,
 
 def block_sparse_fwd(q_perm, k_perm, v_perm, idx, cnt, out_row_map=None, kv_len=None, scale=None,
                      out=None, token_major=False, out_shards: Optional[ShardTable] = None, out_head0: int = 0,
-                     batch: int = 1):
+                     batch: int = 1, fine: Optional[torch.Tensor] = None):
     """bf16 block-sparse attention over permuted [H, L, D] tensors; ``idx=None``
     attends every key block (dense).  ``token_major=True`` stores the result as
     [L, H, D] (the layout the output projection reads) instead of [H, L, D].
 
     ``batch`` > 1: the tensors are [batch * H, L, D], the lists [H, Qb, kmax] are shared by all
     batch elements, and the result is [batch, H, L, D] or, token-major, [batch, L, H, D]
-    (``dfs_block_sparse_fwd_batched``)."""
+    (``dfs_block_sparse_fwd_batched``).  ``fine``: int64 tile maps [H, Qb, kmax] from ``fine_top_p``
+    (``dfs_block_sparse_fwd_fine``); not combined with ``batch`` or ``out_shards``."""
     _need_cuda(q_perm, k_perm, v_perm)
     for t in (q_perm, k_perm, v_perm):
         if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.shape != q_perm.shape:
@@ -225,6 +246,12 @@ def block_sparse_fwd(q_perm, k_perm, v_perm, idx, cnt, out_row_map=None, kv_len=
     batch = int(batch)
     if batch < 1 or H % batch:
         raise ValueError("the leading dimension must be batch * heads")
+    if fine is not None:
+        if batch != 1 or out_shards is not None or idx is None:
+            raise ValueError("tile maps go with plain lists of one batch element on one GPU")
+        if fine.dtype != torch.int64 or not fine.is_contiguous() or tuple(fine.shape) != tuple(idx.shape) \
+                or not fine.is_cuda:
+            raise ValueError("fine must be a contiguous CUDA int64 tensor shaped like idx")
     if batch > 1:
         if out_shards is not None:
             raise ValueError("batched launches do not scatter to sequence shards")
@@ -259,6 +286,13 @@ def block_sparse_fwd(q_perm, k_perm, v_perm, idx, cnt, out_row_map=None, kv_len=
     kv_len = L if kv_len is None else int(kv_len)
     scale = D ** -0.5 if scale is None else float(scale)
     kmax = 0 if idx is None else idx.shape[-1]
+    if fine is not None:
+        check(lib.dfs_block_sparse_fwd_fine(q_perm.data_ptr(), k_perm.data_ptr(), v_perm.data_ptr(), _ptr(idx),
+                                            _ptr(cnt), fine.data_ptr(), kmax, _ptr(out_row_map), out.data_ptr(),
+                                            int(token_major), H, L, kv_len, D, scale,
+                                            status_tensor(q_perm.device).data_ptr(), _stream(q_perm.device)),
+              "dfs_block_sparse_fwd_fine")
+        return out
     check(lib.dfs_block_sparse_fwd_ex(q_perm.data_ptr(), k_perm.data_ptr(), v_perm.data_ptr(), _ptr(idx),
                                       _ptr(cnt), kmax, _ptr(out_row_map), out.data_ptr(), int(token_major),
                                       H, L, kv_len, D, scale, status_tensor(q_perm.device).data_ptr(),

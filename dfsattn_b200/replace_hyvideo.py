@@ -38,10 +38,13 @@ class HunyuanVideo_DFSAttn_Processor2_0:
         if mode == "dfs":
             if sparse_execution != "native":
                 raise ValueError(f"sparse_execution={sparse_execution!r}: only 'native' is built for B200")
-            if selector_mode != "topk" or block_top_p is not None or token_top_k:
-                raise ValueError("only the top-k block selector is built for B200")
+            if selector_mode not in ("topk", "kp") or block_top_p is not None or token_top_k:
+                raise ValueError("the B200 build has the top-k block selector and its kp refinement "
+                                 "(fine top-p inside the chosen blocks)")
             if block_size != 128 or tile_size not in (16, 32, 64):
                 raise ValueError("block_size must be 128 and tile_size 16, 32 or 64")
+            if selector_mode == "kp" and tile_size != 16:
+                raise ValueError("kp mode requires 128x128 coarse blocks and 16x16 sub-blocks")
         for name in other_backend_knobs:
             if not (name.startswith("flashinfer64_") or name.startswith("attention_debug_")):
                 raise TypeError(f"unexpected keyword argument {name!r}")

@@ -245,6 +245,35 @@ int dfs_block_sparse_fwd_ex(const void* q, const void* k, const void* v, const i
                             int out_token_major, int heads, int64_t seq_len, int64_t kv_len,
                             int head_dim, float scale, int32_t* status, void* stream);
 
+/* The "kp" selector: fine top-p inside the chosen block pairs.  Replaces
+ * _refine_topk_mask_with_subblock_top_p (dfsattn/attention_hyvideo.py:211-302, reached from
+ * _compute_block_mask :481-489 when selector_mode == "kp").  Call it right after dfs_block_scores
+ * with the SAME shape arguments and workspace (it reads the pooled means and log-sum-exps left
+ * there) and after dfs_select_topk (it walks the lists).  For every list entry (head, query block,
+ * slot) it writes a 64-bit map, bit 8 * i + j = the 16 x 16-token tile (query tile i, key tile j)
+ * of that 128 x 128 pair is attended: the pair's 64 softmax-ed tile scores are ranked jointly,
+ * largest first, and a tile is kept while the scores ranked before it sum to less than fine_top_p
+ * times the pair's total.  Key blocks >= n_rank (text / boundary columns) and query rows >=
+ * dense_row_start keep whole pairs (all ones, :298-301); slots >= cnt get 0.  tile must be 16.
+ *  idx/cnt   : the lists, int32 [H, q_rows, kmax] / [H, q_rows].
+ *  fine_bits : uint64 [H, q_rows, kmax]. */
+int dfs_fine_top_p(const void* workspace, int64_t workspace_bytes, int heads, int64_t seq_len,
+                   int64_t video_len, int head_dim, int tile, int block, int wan_layout,
+                   const int32_t* idx, const int32_t* cnt, int kmax, int q_rows, int n_rank,
+                   int dense_row_start, float fine_top_p, uint64_t* fine_bits, void* stream);
+
+/* dfs_block_sparse_fwd_ex restricted further to the 16 x 16-token tiles named by the maps of
+ * dfs_fine_top_p (fine_bits: uint64 [H, Qb, kmax], one map per list entry): scores of dropped
+ * tiles are excluded from the softmax.  Replaces kp_fine_sparse_attention as called at
+ * dfsattn/attention_hyvideo.py:968-982 (the reference's Triton kernel over compact 16 x 16 masks,
+ * dfsattn/kernels/triton/kp_flex_attention.py).  The tensor-core work is that of the listed
+ * 128 x 128 blocks; dropped tiles save softmax work only.  A row left without any key gets zeros. */
+int dfs_block_sparse_fwd_fine(const void* q, const void* k, const void* v, const int32_t* idx,
+                              const int32_t* cnt, const uint64_t* fine_bits, int kmax,
+                              const int32_t* out_row_map, void* out, int out_token_major, int heads,
+                              int64_t seq_len, int64_t kv_len, int head_dim, float scale,
+                              int32_t* status, void* stream);
+
 /* Several batch elements that share ONE set of block lists, in one launch: the two
  * classifier-free-guidance passes of a Wan denoising step.  The reference runs them as two
  * successive calls (its processor counts two calls per step, dfsattn/replace_wan.py:253,320-323,

@@ -87,9 +87,13 @@ def test_processor_constructors_keep_the_reference_argument_order():
     assert hp._is_sparse_call()
     hp.skip_layers = [5]
     assert not hp._is_sparse_call()
-    for bad in (dict(sparse_execution="flashinfer64"), dict(selector_mode="kp"), dict(token_top_k=8)):
+    for bad in (dict(sparse_execution="flashinfer64"), dict(selector_mode="top_p"), dict(token_top_k=8)):
         with pytest.raises(ValueError):
             HP("dfs", 0.3, 16, 128, 1024, None, 5, [0], 12, 12, 0.1, True, **bad)
+    kp = HP("dfs", 0.3, 16, 128, 1024, None, 5, [0], 12, 12, 0.1, True, selector_mode="kp", fine_top_p=0.8)
+    assert (kp.selector_mode, kp.fine_top_p) == ("kp", 0.8)
+    with pytest.raises(ValueError):      # the tile maps are 8 x 8: 16-token tiles only
+        HP("dfs", 0.3, 32, 128, 1024, None, 5, [0], 12, 12, 0.1, True, selector_mode="kp")
     with pytest.raises(ValueError):
         HP("dfs", 0.3, 8, 128, 1024, None, 5, [0], 12, 12, 0.1, True)   # tile sizes: 16, 32, 64
 

@@ -33,6 +33,7 @@ def test_call_workload_line():
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["value"] > 0
     assert {"permute_ms", "score_select_ms", "attention_ms", "fused_prepare_ms"} <= set(d["stages"])
     assert "sm_mhz" in d["clocks"] and "reasons" in d["clocks"]
+    assert d["stages"]["kp_attention_ms"] > 0 and 0 < d["stages"]["kp_tiles_kept_frac"] <= 1
 
 
 def test_wan_workload_line_times_the_guidance_pair():

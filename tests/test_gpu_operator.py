@@ -115,7 +115,8 @@ def test_mask_cache_follows_the_schedule():
 def test_unsupported_knobs_raise():
     from dfsattn_b200.attention_hyvideo import dfs_attention
     x = torch.zeros(1, 1, 128, 128, device="cuda", dtype=torch.bfloat16)
-    for bad in (dict(sparse_execution="hybrid"), dict(selector_mode="kp"), dict(block_top_p=0.5),
+    for bad in (dict(sparse_execution="hybrid"), dict(selector_mode="top_p"), dict(block_top_p=0.5),
+                dict(selector_mode="kp", tile_size=32), dict(selector_mode="kp", fine_top_p=0.0),
                 dict(token_top_k=4), dict(block_size=64), dict(tile_size=8)):
         kw = dict(tile_size=16, video_len=128)
         kw.update(bad)
