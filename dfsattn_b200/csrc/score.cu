@@ -496,11 +496,22 @@ extern "C" int dfs_block_scores(const void* q_perm, const void* k_perm, int dtyp
 // tile scores are recomputed from the pooled means and the stored log-sum-exps that the block
 // scoring left in its scratch, ranked jointly (larger first), and a tile is kept while the scores ranked
 // before it sum to less than top_p times the pair's total.  Result: one 64-bit map per list
-// entry, bit 8 * (query tile) + (key tile).  One CTA per (query block, head), one warp per pair.
+// entry, bit 8 * (query tile) + (key tile).  One CTA per (query block, head), one warp per pair;
+// nothing is staged in shared memory except the 8 row normalisers.
 // --------------------------------------------------------------------------
 namespace {
 
 constexpr int kFineWarps = 8;
+
+// D += A . B for a 16 x 8 x 16 bf16 tile with fp32 accumulation; rows 8..15 of A are zero (a1 = a3 = 0),
+// so only c[0], c[1] (row lane / 4, columns 2 * (lane % 4) and + 1) carry results.
+__device__ __forceinline__ void mma_16x8x16_bf16(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
 
 template <int HD>
 __global__ void __launch_bounds__(kFineWarps * 32)
@@ -508,9 +519,6 @@ fine_top_p_kernel(const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __r
                   const float* __restrict__ lse, const int32_t* __restrict__ idx, const int32_t* __restrict__ cnt,
                   unsigned long long* __restrict__ bits, ScoreShape s, int q_rows, int kmax, int n_rank,
                   int dense_row_start, float top_p, float scale_log2) {
-  constexpr int kPad = HD + 4;  // fp32 row pitch in shared memory (rows start 4 banks apart)
-  __shared__ __align__(16) float q_s[8][kPad];
-  __shared__ __align__(16) float k_s[kFineWarps][8][kPad];
   __shared__ float row_lse[8];
   const int head = blockIdx.y, qb = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -534,16 +542,29 @@ fine_top_p_kernel(const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __r
     for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
     if (lane == 0) row_lse[warp] = m + log2f(z);
   }
-  // pooled query rows of this block as fp32 (hi + lo)
-  {
-    const __nv_bfloat16* __restrict__ hi = qm + (static_cast<size_t>(2 * head) * s.nq_pad + qb * 8) * HD;
-    const __nv_bfloat16* __restrict__ lo = hi + static_cast<size_t>(s.nq_pad) * HD;
-    for (int e = threadIdx.x; e < 8 * HD; e += blockDim.x)
-      q_s[e / HD][e % HD] = __bfloat162float(hi[e]) + __bfloat162float(lo[e]);
-  }
   __syncthreads();
 
-  const int qi = lane >> 2, kj0 = (lane & 3) * 2;  // this lane's two tiles: (qi, kj0) and (qi, kj0 + 1)
+  // The 8 x 8 logits of a pair are one 16 x 8 x HD warp-level MMA with the upper 8 rows unused.  In its
+  // fragment layout lane (g = lane / 4, t = lane % 4) holds query row g and key row g at two column
+  // pairs of every 16-column step, straight from the bf16 hi / lo planes, and receives the logits
+  // (query tile g, key tiles 2t and 2t + 1).  Same three products as the block scoring:
+  // hi.hi + hi.lo + lo.hi with fp32 accumulation.
+  // The contraction does not care in which order the columns are visited as long as both operands
+  // visit them in the same order, so a lane takes 16 contiguous bytes (columns 8t .. 8t + 7 of a
+  // 32-column span) per row and plane with one load and feeds them to two MMA steps.
+  constexpr int kSpans = HD / 32;
+  const int g = lane >> 2, t = lane & 3;
+  uint4 qh[kSpans], ql[kSpans];
+  {
+    const __nv_bfloat16* __restrict__ hi = qm + (static_cast<size_t>(2 * head) * s.nq_pad + qb * 8 + g) * HD;
+    const __nv_bfloat16* __restrict__ lo = hi + static_cast<size_t>(s.nq_pad) * HD;
+#pragma unroll
+    for (int sp = 0; sp < kSpans; ++sp) {
+      qh[sp] = __ldg(reinterpret_cast<const uint4*>(hi) + sp * 4 + t);
+      ql[sp] = __ldg(reinterpret_cast<const uint4*>(lo) + sp * 4 + t);
+    }
+  }
+  const int qi = g;  // this lane's two tiles: (qi, 2t) and (qi, 2t + 1)
   const float my_lse = row_lse[qi];
   for (int slot = warp; slot < kmax; slot += kFineWarps) {
     if (slot >= n_list) {
@@ -555,31 +576,25 @@ fine_top_p_kernel(const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __r
       if (lane == 0) bits[list_at + slot] = ~0ull;
       continue;
     }
-    // stage the 8 pooled key rows of the block as fp32
-    const __nv_bfloat16* __restrict__ hi = km + (static_cast<size_t>(2 * head) * s.nk_pad + kb * 8) * HD;
+    const __nv_bfloat16* __restrict__ hi = km + (static_cast<size_t>(2 * head) * s.nk_pad + kb * 8 + g) * HD;
     const __nv_bfloat16* __restrict__ lo = hi + static_cast<size_t>(s.nk_pad) * HD;
-    __syncwarp();
-    for (int e = lane * 4; e < 8 * HD; e += 32 * 4) {  // consecutive lanes, consecutive 16-byte stores
-      const uint2 h4 = __ldg(reinterpret_cast<const uint2*>(hi + e));
-      const uint2 l4 = __ldg(reinterpret_cast<const uint2*>(lo + e));
-      float4 f;
-      f.x = __uint_as_float(h4.x << 16) + __uint_as_float(l4.x << 16);
-      f.y = __uint_as_float(h4.x & 0xffff0000u) + __uint_as_float(l4.x & 0xffff0000u);
-      f.z = __uint_as_float(h4.y << 16) + __uint_as_float(l4.y << 16);
-      f.w = __uint_as_float(h4.y & 0xffff0000u) + __uint_as_float(l4.y & 0xffff0000u);
-      *reinterpret_cast<float4*>(&k_s[warp][e / HD][e % HD]) = f;
+    uint4 kh[kSpans], kl[kSpans];
+#pragma unroll
+    for (int sp = 0; sp < kSpans; ++sp) {
+      kh[sp] = __ldg(reinterpret_cast<const uint4*>(hi) + sp * 4 + t);
+      kl[sp] = __ldg(reinterpret_cast<const uint4*>(lo) + sp * 4 + t);
     }
-    __syncwarp();
-    float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;  // four independent partial sums per logit
-#pragma unroll 8
-    for (int c = 0; c < HD; c += 4) {
-      const float4 qv = *reinterpret_cast<const float4*>(&q_s[qi][c]);
-      const float4 a = *reinterpret_cast<const float4*>(&k_s[warp][kj0][c]);
-      const float4 b = *reinterpret_cast<const float4*>(&k_s[warp][kj0 + 1][c]);
-      s0.x = fmaf(qv.x, a.x, s0.x); s0.y = fmaf(qv.y, a.y, s0.y); s0.z = fmaf(qv.z, a.z, s0.z); s0.w = fmaf(qv.w, a.w, s0.w);
-      s1.x = fmaf(qv.x, b.x, s1.x); s1.y = fmaf(qv.y, b.y, s1.y); s1.z = fmaf(qv.z, b.z, s1.z); s1.w = fmaf(qv.w, b.w, s1.w);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int sp = 0; sp < kSpans; ++sp) {
+      mma_16x8x16_bf16(acc, qh[sp].x, qh[sp].y, kh[sp].x, kh[sp].y);
+      mma_16x8x16_bf16(acc, qh[sp].z, qh[sp].w, kh[sp].z, kh[sp].w);
+      mma_16x8x16_bf16(acc, qh[sp].x, qh[sp].y, kl[sp].x, kl[sp].y);
+      mma_16x8x16_bf16(acc, qh[sp].z, qh[sp].w, kl[sp].z, kl[sp].w);
+      mma_16x8x16_bf16(acc, ql[sp].x, ql[sp].y, kh[sp].x, kh[sp].y);
+      mma_16x8x16_bf16(acc, ql[sp].z, ql[sp].w, kh[sp].z, kh[sp].w);
     }
-    const float d0 = (s0.x + s0.y) + (s0.z + s0.w), d1 = (s1.x + s1.y) + (s1.z + s1.w);
+    const float d0 = acc[0], d1 = acc[1];
     const float v0 = exp2f(fmaf(d0, scale_log2, -my_lse)), v1 = exp2f(fmaf(d1, scale_log2, -my_lse));
     // Rank the 64 scores, largest first, with a bitonic sort over the warp (two per lane).  Key: the
     // score's bits (non-negative floats order like their bit patterns) above 63 - tile index, so equal

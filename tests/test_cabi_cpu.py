@@ -162,3 +162,26 @@ def test_host_entry_point_head_groups_cover_every_head_once():
     sizes = [h1 - h0 for h0, h1 in group_bounds(24, 12)]
     assert sizes[:3] == [1, 1, 1] and sizes[-2:] == [1, 1]      # short first upload, short last download
     assert [h1 - h0 for h0, h1 in group_bounds(24, 12, ramp=False)] == [2] * 12
+
+
+def test_fine_selector_entry_points_reject_bad_arguments_before_any_launch():
+    from dfsattn_b200 import _lib
+    lib = _lib.lib
+    ws, idx, cnt, bits = 0x10000, 0x20000, 0x30000, 0x40000
+    ok = dict(workspace=ws, nbytes=1 << 30, heads=2, L=1024, V=1024, D=128, tile=16, block=128, wan=0, idx=idx,
+              cnt=cnt, kmax=4, q_rows=8, n_rank=8, dense=8, p=0.9, bits=bits)
+
+    def call(**kw):
+        a = dict(ok, **kw)
+        return lib.dfs_fine_top_p(a["workspace"], a["nbytes"], a["heads"], a["L"], a["V"], a["D"], a["tile"],
+                                  a["block"], a["wan"], a["idx"], a["cnt"], a["kmax"], a["q_rows"], a["n_rank"],
+                                  a["dense"], a["p"], a["bits"], None)
+    assert call(idx=None) == -1 and call(bits=None) == -1 and call(workspace=None) == -1
+    assert call(workspace=ws + 16) == -2 and call(bits=bits + 4) == -2
+    assert call(tile=32) == -3                      # the maps are 8 x 8: 16-token tiles only
+    assert call(nbytes=1024) == -6                  # not the scratch of this shape
+    assert call(kmax=0) == -5 and call(q_rows=7) == -5 and call(n_rank=9) == -5 and call(p=0.0) == -5
+    # attention with maps: maps need lists, and 8-byte alignment
+    f = lambda idx_, cnt_, fine_: lib.dfs_block_sparse_fwd_fine(0x1000, 0x2000, 0x3000, idx_, cnt_, fine_, 4, None,
+                                                                0x4000, 0, 2, 256, 256, 128, 0.1, None, None)
+    assert f(idx, cnt, None) == -1 and f(None, None, bits) == -1 and f(idx, cnt, bits + 4) == -2

@@ -111,3 +111,47 @@ def test_fused_prepare_rows_against_the_oracle_arithmetic(full):
         assert float(diff.max()) <= 0.07, float(diff.max())
         assert float((diff > 0).float().mean()) <= 5e-3
     assert torch.equal(got[2][:, rows], want[2])
+
+
+def test_kp_tile_maps_at_full_size(full):
+    """The kp selector on the full shape: dense policy exact, every refined pair keeps a top set of its
+    64 tile scores whose mass just reaches fine_top_p (checked for whole query-block rows against fp32
+    arithmetic on the pooled means), and the attention under the maps still has softmax mass one."""
+    from dfsattn_b200 import engine
+    ops, q, k = full["ops"], full["q"], full["k"]
+    P = 0.9
+    perm, _ = oracle.build_permutation(full["vperm"], L, VIDEO)
+    p32 = perm.to(torch.int32).cuda()
+    qp, kp, vp = ops.permute_qkv(q[0], k[0], torch.ones_like(q[0]), p32)
+    lists = engine.compute_block_lists(qp, kp, VIDEO, SPARSITY, "hyvideo", tile=16, fine_top_p=P)
+    assert torch.equal(lists.idx, full["lists"].idx) and lists.fine.shape == lists.idx.shape
+    fine = lists.fine
+    assert bool((fine[:, DENSE_START:] == -1).all())                       # dense rows: whole blocks
+    assert bool((fine[:, :DENSE_START, K_SEL - 3:K_SEL] == -1).all())      # forced text / boundary columns
+    assert bool((fine[:, :DENSE_START, K_SEL:] == 0).all())                # unused slots
+    refined = fine[:, :DENSE_START, :K_SEL - 3]
+    assert bool((refined != 0).all())                                      # the largest tile always stays
+    shifts = torch.arange(64, device="cuda", dtype=torch.int64)
+    scale = D ** -0.5
+    for head, qb in ((0, 0), (7, 411), (23, DENSE_START - 1)):
+        # pooled fp32 means of this query block and of all keys (scoring layout: video | gap | text)
+        qm = qp[head, qb * 128:(qb + 1) * 128].float().view(8, 16, D).mean(1)
+        kv = torch.zeros((KB * 128, D), device="cuda")
+        kv[:VIDEO] = kp[head, :VIDEO].float()
+        kv[(DENSE_START + 1) * 128:(DENSE_START + 1) * 128 + TEXT] = kp[head, VIDEO:].float()
+        km = kv.view(KB * 8, 16, D).mean(1)
+        score = torch.softmax((qm @ km.T) * scale, -1).view(8, KB, 8)       # [q tile, key block, key tile]
+        blocks = lists.idx[head, qb, :K_SEL - 3].long()
+        vals = score[:, blocks].permute(1, 0, 2).reshape(-1, 64)            # [pair, 8 * i + j]
+        keep = ((refined[head, qb, :, None] >> shifts) & 1).bool()
+        total = vals.sum(-1)
+        kept_mass = (vals * keep).sum(-1)
+        smallest_kept = vals.masked_fill(~keep, float("inf")).min(-1).values
+        largest_dropped = vals.masked_fill(keep, 0.0).max(-1).values
+        tol = 1e-4 * total
+        assert bool((smallest_kept + tol >= largest_dropped).all())         # a top set
+        assert bool((kept_mass + tol >= P * total).all())                   # reaches the mass ...
+        assert bool((kept_mass - smallest_kept - tol < P * total).all())    # ... and not with one tile less
+    out = ops.block_sparse_fwd(qp, kp, vp, lists.idx, lists.cnt, out_row_map=p32, fine=lists.fine)
+    assert float((out.float() - 1).abs().max()) <= 1e-2
+    ops.check_status("cuda")
