@@ -496,8 +496,7 @@ extern "C" int dfs_block_scores(const void* q_perm, const void* k_perm, int dtyp
 // tile scores are recomputed from the pooled means and the stored log-sum-exps that the block
 // scoring left in its scratch, ranked jointly (larger first), and a tile is kept while the scores ranked
 // before it sum to less than top_p times the pair's total.  Result: one 64-bit map per list
-// entry, bit 8 * (query tile) + (key tile).  One CTA per (query block, head), one warp per pair;
-// nothing is staged in shared memory except the 8 row normalisers.
+// entry, bit 8 * (query tile) + (key tile).  One CTA per (query block, head), one warp per pair.
 // --------------------------------------------------------------------------
 namespace {
 
@@ -514,12 +513,13 @@ __device__ __forceinline__ void mma_16x8x16_bf16(float (&c)[4], uint32_t a0, uin
 }
 
 template <int HD>
-__global__ void __launch_bounds__(kFineWarps * 32)
+__global__ void __launch_bounds__(kFineWarps * 32, 3)
 fine_top_p_kernel(const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __restrict__ km,
                   const float* __restrict__ lse, const int32_t* __restrict__ idx, const int32_t* __restrict__ cnt,
                   unsigned long long* __restrict__ bits, ScoreShape s, int q_rows, int kmax, int n_rank,
                   int dense_row_start, float top_p, float scale_log2) {
   __shared__ float row_lse[8];
+  __shared__ uint4 q_s[2][8][HD / 8 + 4];
   const int head = blockIdx.y, qb = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const size_t list_at = (static_cast<size_t>(head) * q_rows + qb) * kmax;
@@ -554,45 +554,57 @@ fine_top_p_kernel(const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __r
   // 32-column span) per row and plane with one load and feeds them to two MMA steps.
   constexpr int kSpans = HD / 32;
   const int g = lane >> 2, t = lane & 3;
-  uint4 qh[kSpans], ql[kSpans];
-  {
-    const __nv_bfloat16* __restrict__ hi = qm + (static_cast<size_t>(2 * head) * s.nq_pad + qb * 8 + g) * HD;
-    const __nv_bfloat16* __restrict__ lo = hi + static_cast<size_t>(s.nq_pad) * HD;
-#pragma unroll
-    for (int sp = 0; sp < kSpans; ++sp) {
-      qh[sp] = __ldg(reinterpret_cast<const uint4*>(hi) + sp * 4 + t);
-      ql[sp] = __ldg(reinterpret_cast<const uint4*>(lo) + sp * 4 + t);
-    }
+  // The pooled query rows (both planes) wait in shared memory, 320-byte row pitch: the eight lanes of a
+  // 16-byte access phase (two rows) then fall on different banks.
+  for (int e = threadIdx.x; e < 2 * 8 * (HD / 8); e += blockDim.x) {
+    const int plane = e / (8 * (HD / 8)), row = (e / (HD / 8)) % 8, c = e % (HD / 8);
+    const __nv_bfloat16* src = qm + (static_cast<size_t>(2 * head + plane) * s.nq_pad + qb * 8 + row) * HD;
+    q_s[plane][row][c] = __ldg(reinterpret_cast<const uint4*>(src) + c);
   }
+  // Lists are ascending (dfs_select_topk writes them so): the refinable entries, key blocks below
+  // n_rank, are a prefix of the list.
+  int n_ref = 0;
+  for (int base = 0; base < n_list; base += blockDim.x) {
+    const int slot = base + threadIdx.x;
+    n_ref += __syncthreads_count(slot < n_list && idx[list_at + slot] < n_rank);
+  }
+  __syncthreads();
+  for (int slot = n_ref + threadIdx.x; slot < kmax; slot += blockDim.x)
+    bits[list_at + slot] = slot < n_list ? ~0ull : 0ull;  // forced (text / boundary) blocks stay whole; unused slots
+
   const int qi = g;  // this lane's two tiles: (qi, 2t) and (qi, 2t + 1)
   const float my_lse = row_lse[qi];
-  for (int slot = warp; slot < kmax; slot += kFineWarps) {
-    if (slot >= n_list) {
-      if (lane == 0) bits[list_at + slot] = 0ull;
-      continue;
-    }
+  // operands of the NEXT pair are requested before the current pair is ranked
+  uint4 nh[kSpans], nl[kSpans];
+  auto request = [&](int slot) {
     const int kb = idx[list_at + slot];
-    if (kb >= n_rank) {  // forced (text / boundary) key blocks stay whole
-      if (lane == 0) bits[list_at + slot] = ~0ull;
-      continue;
-    }
     const __nv_bfloat16* __restrict__ hi = km + (static_cast<size_t>(2 * head) * s.nk_pad + kb * 8 + g) * HD;
     const __nv_bfloat16* __restrict__ lo = hi + static_cast<size_t>(s.nk_pad) * HD;
+#pragma unroll
+    for (int sp = 0; sp < kSpans; ++sp) {
+      nh[sp] = __ldg(reinterpret_cast<const uint4*>(hi) + sp * 4 + t);
+      nl[sp] = __ldg(reinterpret_cast<const uint4*>(lo) + sp * 4 + t);
+    }
+  };
+  if (warp < n_ref) request(warp);
+  for (int slot = warp; slot < n_ref; slot += kFineWarps) {
     uint4 kh[kSpans], kl[kSpans];
 #pragma unroll
     for (int sp = 0; sp < kSpans; ++sp) {
-      kh[sp] = __ldg(reinterpret_cast<const uint4*>(hi) + sp * 4 + t);
-      kl[sp] = __ldg(reinterpret_cast<const uint4*>(lo) + sp * 4 + t);
+      kh[sp] = nh[sp];
+      kl[sp] = nl[sp];
     }
+    if (slot + kFineWarps < n_ref) request(slot + kFineWarps);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int sp = 0; sp < kSpans; ++sp) {
-      mma_16x8x16_bf16(acc, qh[sp].x, qh[sp].y, kh[sp].x, kh[sp].y);
-      mma_16x8x16_bf16(acc, qh[sp].z, qh[sp].w, kh[sp].z, kh[sp].w);
-      mma_16x8x16_bf16(acc, qh[sp].x, qh[sp].y, kl[sp].x, kl[sp].y);
-      mma_16x8x16_bf16(acc, qh[sp].z, qh[sp].w, kl[sp].z, kl[sp].w);
-      mma_16x8x16_bf16(acc, ql[sp].x, ql[sp].y, kh[sp].x, kh[sp].y);
-      mma_16x8x16_bf16(acc, ql[sp].z, ql[sp].w, kh[sp].z, kh[sp].w);
+      const uint4 qh = q_s[0][g][sp * 4 + t], ql = q_s[1][g][sp * 4 + t];
+      mma_16x8x16_bf16(acc, qh.x, qh.y, kh[sp].x, kh[sp].y);
+      mma_16x8x16_bf16(acc, qh.z, qh.w, kh[sp].z, kh[sp].w);
+      mma_16x8x16_bf16(acc, qh.x, qh.y, kl[sp].x, kl[sp].y);
+      mma_16x8x16_bf16(acc, qh.z, qh.w, kl[sp].z, kl[sp].w);
+      mma_16x8x16_bf16(acc, ql.x, ql.y, kh[sp].x, kh[sp].y);
+      mma_16x8x16_bf16(acc, ql.z, ql.w, kh[sp].z, kh[sp].w);
     }
     const float d0 = acc[0], d1 = acc[1];
     const float v0 = exp2f(fmaf(d0, scale_log2, -my_lse)), v1 = exp2f(fmaf(d1, scale_log2, -my_lse));
