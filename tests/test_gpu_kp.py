@@ -155,3 +155,49 @@ def test_kp_is_refused_where_it_does_not_apply():
         attention_wan.dfs_attention(x, x, x, tile_size=16, selector_mode="kp")      # no such knob on the Wan operator
     with pytest.raises(ValueError):
         dfs_attention(x, x, x, tile_size=32, video_len=256, selector_mode="kp")
+
+
+class _Attn(torch.nn.Module):
+    """Duck-typed stand-in for a diffusers Attention block with per-head RMSNorms."""
+
+    def __init__(self, dim, heads, head_dim):
+        super().__init__()
+        self.heads = heads
+        self.to_q, self.to_k, self.to_v = (torch.nn.Linear(dim, dim) for _ in range(3))
+        self.norm_q, self.norm_k = (torch.nn.RMSNorm(head_dim, eps=1e-6) for _ in range(2))
+        self.to_out = torch.nn.ModuleList([torch.nn.Linear(dim, dim), torch.nn.Identity()])
+        self.add_q_proj = self.add_k_proj = self.add_v_proj = None
+        self.norm_added_q = self.norm_added_k = None
+        self.to_add_out = None
+
+
+def test_hyvideo_processor_runs_the_kp_selector_on_both_paths():
+    """The processor hands selector_mode / fine_top_p through; its fused path (token-major result, inputs
+    already permuted) and its step-by-step path give the same result under the same tile maps."""
+    from dfsattn_b200.replace_hyvideo import HunyuanVideo_DFSAttn_Processor2_0 as P
+    from dfsattn_b200.attention_hyvideo import DFS_Attention
+    from dfsattn_b200.order import hilbert3d_perm
+    torch.manual_seed(3)
+    grid, text, heads, D = (3, 8, 16), 64, 2, 128
+    V = grid[0] * grid[1] * grid[2]
+    attn = _Attn(heads * D, heads, D).cuda().bfloat16()
+    hs = torch.randn(1, V, heads * D, device="cuda", dtype=torch.bfloat16)
+    enc = torch.randn(1, text, heads * D, device="cuda", dtype=torch.bfloat16)
+    am = torch.ones(1, V + text, dtype=torch.bool, device="cuda")
+    ang = torch.rand(V, D // 2, device="cuda") * 6.28
+    rope = (ang.cos().repeat_interleave(2, 1), ang.sin().repeat_interleave(2, 1))
+    args = ("dfs", 0.75, 16, 128, V, hilbert3d_perm(*grid), 3, [], 1, 4, 0.0, True)
+    slow, fast = (P(*args, selector_mode="kp", fine_top_p=0.8) for _ in range(2))
+    slow.fused_prepare = False
+    slow.step_idx = 1                           # refresh: lists and tile maps from the step-by-step inputs
+    o1, e1 = slow(attn, hs, enc, attention_mask=am, image_rotary_emb=rope)
+    (key, entry), = DFS_Attention._cached_metadata.items()
+    assert key[8] == "kp" and key[9] == 0.8 and entry["block_lists"].fine is not None
+    fine = entry["block_lists"].fine
+    assert bool((fine != -1).any())             # something was dropped
+    fast.step_idx = 2                           # reuse step: the same maps
+    o2, e2 = fast(attn, hs, enc, attention_mask=am, image_rotary_emb=rope)
+    assert fast.last_call_fused and not slow.last_call_fused
+    for a, b in ((o1, o2), (e1, e2)):
+        m = oracle.tensor_metrics(a.detach().float().cpu(), b.detach().float().cpu())
+        assert m["cosine"] >= 0.9995 and m["max_abs"] <= 6e-2, m
