@@ -620,9 +620,9 @@ fine_top_p_kernel(const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __r
       for (int j = k >> 1; j > 0; j >>= 1) {
         if (j == 1) {  // the partner is the lane's other element
           const bool swap = desc ? (k0 < k1) : (k0 > k1);
-          const unsigned long long lo_key = swap ? k1 : k0, hi_key = swap ? k0 : k1;
-          k0 = lo_key;
-          k1 = hi_key;
+          const unsigned long long first = swap ? k1 : k0, second = swap ? k0 : k1;
+          k0 = first;
+          k1 = second;
         } else {
           const unsigned long long o0 = __shfl_xor_sync(0xffffffffu, k0, j >> 1);
           const unsigned long long o1 = __shfl_xor_sync(0xffffffffu, k1, j >> 1);

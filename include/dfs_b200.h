@@ -255,7 +255,8 @@ int dfs_block_sparse_fwd_ex(const void* q, const void* k, const void* v, const i
  * largest first, and a tile is kept while the scores ranked before it sum to less than fine_top_p
  * times the pair's total.  Key blocks >= n_rank (text / boundary columns) and query rows >=
  * dense_row_start keep whole pairs (all ones, :298-301); slots >= cnt get 0.  tile must be 16.
- *  idx/cnt   : the lists, int32 [H, q_rows, kmax] / [H, q_rows].
+ *  idx/cnt   : the lists, int32 [H, q_rows, kmax] / [H, q_rows], each list ascending (as
+ *              dfs_select_topk writes them: the refinable entries are then a prefix).
  *  fine_bits : uint64 [H, q_rows, kmax]. */
 int dfs_fine_top_p(const void* workspace, int64_t workspace_bytes, int heads, int64_t seq_len,
                    int64_t video_len, int head_dim, int tile, int block, int wan_layout,
