@@ -174,10 +174,7 @@ class DFS_Attention(nn.Module):
         cls = type(self)
         if lists.fine is not None:
             # kp: density of the 16 x 16-token mask (the reference counts with logical_block_size 16, :1243)
-            fine = lists.to_fine_mask(seq_len)
-            size = torch.full((fine.shape[1],), 16.0, dtype=torch.float64, device=fine.device)
-            size[-1] = seq_len - 16 * (fine.shape[1] - 1)
-            pairs = int((fine.double() * size[None, :, None] * size[None, None, :]).sum().item())
+            pairs = lists.fine_pair_count(seq_len)
         else:
             pairs = ops.interaction_count(lists.idx, lists.cnt, lists.idx.shape[0], seq_len, self.block_size)
         total = lists.idx.shape[0] * seq_len * seq_len

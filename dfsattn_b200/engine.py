@@ -31,6 +31,27 @@ class BlockLists:
         return BlockLists(self.idx.clone(), self.cnt.clone(), self.k_blocks,
                           None if self.fine is None else self.fine.clone())
 
+    def fine_pair_count(self, seq_len: int) -> int:
+        """Attended (q, k) token pairs under the tile maps, partial last blocks included, without
+        building the 16 x 16 mask: an all-ones map is a whole block (counted with its true row and
+        column sizes), any other map belongs to a pair of full 128-token blocks (refined pairs lie
+        before the boundary block) and counts 256 pairs per set bit."""
+        if self.fine is None:
+            raise ValueError("no tile maps")
+        H, Qb, kmax = self.idx.shape
+        dev = self.idx.device
+        valid = self.idx >= 0
+        whole = valid & (self.fine == -1)
+        size = torch.full((self.k_blocks + 1,), BLOCK, dtype=torch.int64, device=dev)
+        size[self.k_blocks - 1] = seq_len - BLOCK * (self.k_blocks - 1)
+        size[self.k_blocks] = 0
+        cols = size[torch.where(valid, self.idx, torch.full_like(self.idx, self.k_blocks)).long()]
+        pairs = int((size[None, :Qb] * (cols * whole).sum(-1)).sum().item())
+        lut = torch.tensor([bin(i).count("1") for i in range(256)], dtype=torch.int64, device=dev)
+        part = (valid & ~whole)[..., None].expand(-1, -1, -1, 8)
+        set_bits = int((lut[self.fine.view(torch.uint8).view(H, Qb, kmax, 8).long()] * part).sum().item())
+        return pairs + 256 * set_bits
+
     def to_fine_mask(self, seq_len: int) -> torch.Tensor:
         """bool [H, ceil(L/16), ceil(L/16)]: the reference's fine mask format
         (dfsattn/attention_hyvideo.py:236-241), for inspection and tests."""

@@ -185,3 +185,26 @@ def test_fine_selector_entry_points_reject_bad_arguments_before_any_launch():
     f = lambda idx_, cnt_, fine_: lib.dfs_block_sparse_fwd_fine(0x1000, 0x2000, 0x3000, idx_, cnt_, fine_, 4, None,
                                                                 0x4000, 0, 2, 256, 256, 128, 0.1, None, None)
     assert f(idx, cnt, None) == -1 and f(None, None, bits) == -1 and f(idx, cnt, bits + 4) == -2
+
+
+def test_pair_count_under_tile_maps_equals_the_count_on_the_expanded_mask():
+    """Host logic of the kp density record: counting from the 64-bit maps (whole blocks with their
+    true sizes, refined pairs 256 per bit) against the 16 x 16 mask built out of the same maps."""
+    import math
+    from dfsattn_b200.engine import BlockLists
+    torch.manual_seed(0)
+    for L in (1000, 1024, 935):
+        kb = math.ceil(L / 128)
+        mask = torch.rand(2, kb, kb) > 0.4
+        mask[:, :, 0] = True
+        lists = BlockLists.from_bool_mask(mask)
+        dense_start = L // 128
+        fine = torch.randint(-2 ** 63, 2 ** 63 - 1, lists.idx.shape, dtype=torch.int64)
+        refined = (torch.arange(kb)[None, :, None] < dense_start) & (lists.idx < dense_start) & (lists.idx >= 0)
+        lists.fine = torch.where(refined, fine, torch.full_like(fine, -1))
+        lists.fine[0, 0, 0] = -1                      # a refined pair that kept every tile
+        fm = lists.to_fine_mask(L)
+        size = torch.full((fm.shape[1],), 16.0, dtype=torch.float64)
+        size[-1] = L - 16 * (fm.shape[1] - 1)
+        want = int((fm.double() * size[None, :, None] * size[None, None, :]).sum().item())
+        assert lists.fine_pair_count(L) == want
