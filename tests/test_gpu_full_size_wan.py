@@ -1,5 +1,6 @@
 """GPU: the whole path at the two full Wan2.1 shapes of the benchmark configurations (480p: 32 760
-tokens, 720p: 75 600 tokens; 40 heads, D = 128, sparsity 0.3; both end in a ragged block), checked
+tokens, 720p: 75 600 tokens, in Hilbert and in raster order; 40 heads, D = 128, sparsity 0.3; both end in
+a ragged block), checked
 through properties that do not need a CPU pass over all heads, plus one head's mask against the CPU
 oracle and the batched guidance pair against the two calls it stands for."""
 import math
@@ -12,7 +13,7 @@ import oracle
 pytestmark = pytest.mark.gpu
 
 HEADS, D, SPARSITY = 40, 128, 0.3
-GRIDS = {"wan_480p": (21, 30, 52), "wan_720p": (21, 45, 80)}
+GRIDS = {"wan_480p": (21, 30, 52), "wan_720p": (21, 45, 80), "wan_720p_raster": (21, 45, 80)}
 
 
 @pytest.fixture(scope="module", params=list(GRIDS))
@@ -29,7 +30,7 @@ def full(request):
     wan.DFS_Attention.clear_cache()
     wan._dfs_attention_instances.clear()
     q, k, v = structured_qkv(grid, HEADS, D, text_len=0, dtype=torch.bfloat16, device="cuda", seed=0)
-    vperm = hilbert3d_perm(*grid)
+    vperm = None if request.param.endswith("raster") else hilbert3d_perm(*grid)   # raster: no gather at all
     kw = dict(skip_steps=12, cache_interval=12, layer_idx=0, sparsity=SPARSITY, sparsity_dcrt=0.1,
               tile_size=16, block_size=128, video_perm=vperm)
     out = wan.dfs_attention(q, k, v, step_idx=24, **kw)
