@@ -608,32 +608,33 @@ fine_top_p_kernel(const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __r
     }
     const float d0 = acc[0], d1 = acc[1];
     const float v0 = exp2f(fmaf(d0, scale_log2, -my_lse)), v1 = exp2f(fmaf(d1, scale_log2, -my_lse));
-    // Rank the 64 scores, largest first, with a bitonic sort over the warp (two per lane).  Key: the
-    // score's bits (non-negative floats order like their bit patterns) above 63 - tile index, so equal
-    // scores rank by index and every key is distinct.
-    unsigned long long k0 = (static_cast<unsigned long long>(__float_as_uint(v0)) << 32) | static_cast<unsigned>(63 - 2 * lane);
-    unsigned long long k1 = (static_cast<unsigned long long>(__float_as_uint(v1)) << 32) | static_cast<unsigned>(62 - 2 * lane);
+    // Rank the 64 scores, largest first, with a bitonic sort over the warp (two per lane) on their bit
+    // patterns (non-negative floats order like unsigned integers).  Only the values travel: the kept
+    // tiles are the ranks whose preceding mass is below the limit, i.e. all scores down to the
+    // smallest kept one, which every lane then compares with the two scores it still holds.  (Scores
+    // exactly equal to that smallest kept one are all kept.)
+    const uint32_t u0 = __float_as_uint(v0), u1 = __float_as_uint(v1);
+    uint32_t k0 = u0, k1 = u1;
 #pragma unroll
     for (int k = 2; k <= 64; k <<= 1) {
       const bool desc = ((2 * lane) & k) == 0;  // direction of this element's block in this round
 #pragma unroll
       for (int j = k >> 1; j > 0; j >>= 1) {
         if (j == 1) {  // the partner is the lane's other element
-          const bool swap = desc ? (k0 < k1) : (k0 > k1);
-          const unsigned long long first = swap ? k1 : k0, second = swap ? k0 : k1;
-          k0 = first;
-          k1 = second;
+          const uint32_t big = max(k0, k1), small = min(k0, k1);
+          k0 = desc ? big : small;
+          k1 = desc ? small : big;
         } else {
-          const unsigned long long o0 = __shfl_xor_sync(0xffffffffu, k0, j >> 1);
-          const unsigned long long o1 = __shfl_xor_sync(0xffffffffu, k1, j >> 1);
+          const uint32_t o0 = __shfl_xor_sync(0xffffffffu, k0, j >> 1);
+          const uint32_t o1 = __shfl_xor_sync(0xffffffffu, k1, j >> 1);
           const bool take_max = (((lane & (j >> 1)) == 0) == desc);
-          k0 = take_max ? (k0 > o0 ? k0 : o0) : (k0 < o0 ? k0 : o0);
-          k1 = take_max ? (k1 > o1 ? k1 : o1) : (k1 < o1 ? k1 : o1);
+          k0 = take_max ? max(k0, o0) : min(k0, o0);
+          k1 = take_max ? max(k1, o1) : min(k1, o1);
         }
       }
     }
     // rank 2 * lane holds k0, rank 2 * lane + 1 holds k1: mass ranked before each of them
-    const float a = __uint_as_float(static_cast<uint32_t>(k0 >> 32)), b = __uint_as_float(static_cast<uint32_t>(k1 >> 32));
+    const float a = __uint_as_float(k0), b = __uint_as_float(k1);
     float inc = a + b;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -642,12 +643,12 @@ fine_top_p_kernel(const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __r
     }
     const float before0 = inc - (a + b), before1 = before0 + a;
     const float limit = __shfl_sync(0xffffffffu, inc, 31) * top_p;
-    const int i0 = 63 - static_cast<int>(k0 & 63ull), i1 = 63 - static_cast<int>(k1 & 63ull);
-    uint32_t lo_bits = 0u, hi_bits = 0u;
-    if (before0 < limit) (i0 < 32 ? lo_bits : hi_bits) |= 1u << (i0 & 31);
-    if (before1 < limit) (i1 < 32 ? lo_bits : hi_bits) |= 1u << (i1 & 31);
-    const uint32_t word = __reduce_or_sync(0xffffffffu, lo_bits);
-    const uint32_t hi_word = __reduce_or_sync(0xffffffffu, hi_bits);
+    // smallest kept score (rank 0 is always kept: nothing precedes it)
+    const uint32_t mine = before1 < limit ? k1 : (before0 < limit ? k0 : 0xffffffffu);
+    const uint32_t cutoff = __reduce_min_sync(0xffffffffu, mine);
+    const uint32_t pair_bits = (u0 >= cutoff ? 1u : 0u) | (u1 >= cutoff ? 2u : 0u);  // tiles 2 * lane, 2 * lane + 1
+    const uint32_t half = __reduce_or_sync(lane < 16 ? 0x0000ffffu : 0xffff0000u, pair_bits << (2 * (lane & 15)));
+    const uint32_t word = __shfl_sync(0xffffffffu, half, 0), hi_word = __shfl_sync(0xffffffffu, half, 16);
     if (lane == 0) bits[list_at + slot] = (static_cast<unsigned long long>(hi_word) << 32) | word;
   }
 }
