@@ -519,7 +519,7 @@ def run_gpu(args, spec, rank, local_rank, world):
         stages["kp_attention_ms"] = 1e3 * reduce(t_kp_attn, dist.ReduceOp.MAX if world > 1 else None)
         bytes8 = kp_lists.fine.view(torch.uint8)
         kept = sum(int(((bytes8 >> b) & 1).sum()) for b in range(8))
-        stages["kp_tiles_kept_frac"] = kept / (64.0 * int(kp_lists.cnt.sum()))
+        stages["kp_tiles_kept_frac"] = kept / (64.0 * int(kp_lists.cnt.clamp(min=0).sum()))
         del kp_lists, bytes8
 
     # The processor-side fused step that makes the permute above unnecessary: projections

@@ -75,7 +75,7 @@ struct SmemLayout {
 
 struct Params {
   const int32_t* idx;   // [H, Qb, kmax] or nullptr (all key blocks)
-  const int32_t* cnt;   // [H, Qb]
+  const int32_t* cnt;   // [H, Qb]; -1 = every key block
   // [H, Qb, kmax] or nullptr: per listed block a 64-bit map of its 16 x 16-token tiles, bit 8 * i + j =
   // (query tile i, key tile j) is attended; read only by the kFine instantiation
   const unsigned long long* fine;
@@ -285,9 +285,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int head = blockIdx.y;                 // row of the Q/K/V tensors
   const int group = head / p.list_heads;       // batch element
   const int lhead = head - group * p.list_heads;  // head within the batch element: lists and output
-  const int n_tiles = p.idx ? p.cnt[static_cast<size_t>(lhead) * p.q_blocks + qb] : p.k_blocks;
+  // a negative count marks a row that attends every key block (no list is read for it)
+  const int listed = p.idx ? p.cnt[static_cast<size_t>(lhead) * p.q_blocks + qb] : -1;
+  const int n_tiles = listed >= 0 ? listed : p.k_blocks;
   const int32_t* __restrict__ my_idx =
-      p.idx ? p.idx + (static_cast<size_t>(lhead) * p.q_blocks + qb) * p.kmax : nullptr;
+      listed >= 0 ? p.idx + (static_cast<size_t>(lhead) * p.q_blocks + qb) * p.kmax : nullptr;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);

@@ -117,6 +117,10 @@ extern "C" int64_t dfs_interaction_count(const int32_t* idx, const int32_t* cnt,
       }
       const size_t at = static_cast<size_t>(hh) * q_blocks + r;
       const int n = cnt[at];
+      if (n == -1) {  // a row that attends every key block
+        pairs += rows * seq_len;
+        continue;
+      }
       if (n < 0 || n > kmax) return DFS_ERR_RANGE;
       for (int j = 0; j < n; ++j) {
         const int c = idx[at * kmax + j];

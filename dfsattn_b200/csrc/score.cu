@@ -523,7 +523,8 @@ fine_top_p_kernel(const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __r
   const int head = blockIdx.y, qb = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const size_t list_at = (static_cast<size_t>(head) * q_rows + qb) * kmax;
-  const int n_list = cnt[static_cast<size_t>(head) * q_rows + qb];
+  const int listed = cnt[static_cast<size_t>(head) * q_rows + qb];
+  const int n_list = listed > 0 ? listed : 0;  // -1 (a row that attends every block) has no list: maps unused
   const bool dense_row = qb >= dense_row_start || qb >= s.q_blocks;
   if (dense_row) {  // rows from the first boundary block on keep whole blocks
     for (int slot = threadIdx.x; slot < kmax; slot += blockDim.x) bits[list_at + slot] = slot < n_list ? ~0ull : 0ull;

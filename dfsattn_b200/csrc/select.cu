@@ -10,7 +10,9 @@
 //      tie rule);
 //   3. columns at or past n_rank are always selected ("forced": the text /
 //      boundary key blocks); rows at or past dense_row_start select every
-//      column;
+//      column: when kmax has room for every column they are listed, otherwise
+//      the row gets the count -1 ("every key block") and no list, so that a few
+//      dense rows do not set the list length of all the others;
 //   4. the list is written in ascending column order by an ordered warp
 //      compaction (ballot + popc), padded with -1.
 #include "common.cuh"
@@ -41,6 +43,13 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32)
       mask_out ? mask_out + (static_cast<size_t>(head) * q_rows + row) * n_cols : nullptr;
   const bool dense = row >= dense_row_start;
   const unsigned lt_mask = (1u << lane) - 1u;
+  if (dense && kmax < n_cols) {  // marker row: every key block, nothing listed
+    for (int pos = lane; pos < kmax; pos += 32) out[pos] = -1;
+    if (mrow)
+      for (int c = lane; c < n_cols; c += 32) mrow[c] = 1;
+    if (lane == 0) cnt[static_cast<size_t>(head) * q_rows + row] = -1;
+    return;
+  }
 
   uint32_t thr = 0;  // key of the k-th largest candidate
   int need_eq = 0;   // how many candidates equal to it are selected
@@ -94,10 +103,9 @@ extern "C" int dfs_select_topk(const float* scores, int heads, int score_rows, i
   if (dense_row_start < 0) return DFS_ERR_RANGE;
   if (dense_row_start > q_rows) dense_row_start = q_rows;
   if (dense_row_start > score_rows) return DFS_ERR_RANGE;  // a ranked row needs its scores
-  // every list must fit
+  // every ranked row's list must fit; dense rows are listed only when kmax >= n_cols (else count -1)
   const int sparse_cnt = k_select + (n_cols - n_rank);
-  const int need = dense_row_start < q_rows ? n_cols : sparse_cnt;
-  if (kmax < need || kmax < sparse_cnt) return DFS_ERR_RANGE;
+  if (kmax < sparse_cnt || kmax <= 0) return DFS_ERR_RANGE;
   // one warp per row, its keys in shared memory: fewer warps per CTA for very long rows
   const size_t row_bytes = sizeof(uint32_t) * static_cast<size_t>(n_rank > 0 ? n_rank : 1);
   if (row_bytes > 200 * 1024) return DFS_ERR_SHAPE;

@@ -21,7 +21,7 @@ BLOCK = ops.BLOCK
 class BlockLists:
     """Selected key blocks per (head, query block): ascending lists."""
     idx: torch.Tensor  # int32 [H, Qb, kmax], -1 padded
-    cnt: torch.Tensor  # int32 [H, Qb]
+    cnt: torch.Tensor  # int32 [H, Qb]; -1 = the row attends every key block (nothing listed)
     k_blocks: int
     # "kp" selector only: int64 [H, Qb, kmax], per list entry the 8 x 8 map of attended 16 x 16-token
     # tiles (bit 8 * query tile + key tile); None = whole blocks
@@ -46,7 +46,9 @@ class BlockLists:
         size[self.k_blocks - 1] = seq_len - BLOCK * (self.k_blocks - 1)
         size[self.k_blocks] = 0
         cols = size[torch.where(valid, self.idx, torch.full_like(self.idx, self.k_blocks)).long()]
-        pairs = int((size[None, :Qb] * (cols * whole).sum(-1)).sum().item())
+        per_row = torch.where(self.cnt < 0, torch.full_like(self.cnt, seq_len, dtype=torch.int64),
+                              (cols * whole).sum(-1))
+        pairs = int((size[None, :Qb] * per_row).sum().item())
         lut = torch.tensor([bin(i).count("1") for i in range(256)], dtype=torch.int64, device=dev)
         part = (valid & ~whole)[..., None].expand(-1, -1, -1, 8)
         set_bits = int((lut[self.fine.view(torch.uint8).view(H, Qb, kmax, 8).long()] * part).sum().item())
@@ -66,6 +68,7 @@ class BlockLists:
             safe = torch.where(self.idx >= 0, self.idx, torch.full_like(self.idx, self.k_blocks)).long()
             dense.scatter_(2, safe[..., None, None].expand(-1, -1, -1, 8, 8), tiles)
             full = dense[:, :, : self.k_blocks].permute(0, 1, 3, 2, 4).reshape(H, Qb * 8, self.k_blocks * 8)
+        full = full | (self.cnt < 0).repeat_interleave(8, 1)[..., None]
         nf = math.ceil(seq_len / 16)
         return full[:, :nf, :nf]
 
@@ -75,7 +78,7 @@ class BlockLists:
         mask = torch.zeros((H, Qb, self.k_blocks + 1), dtype=torch.bool, device=self.idx.device)
         safe = torch.where(self.idx >= 0, self.idx, torch.full_like(self.idx, self.k_blocks)).long()
         mask.scatter_(-1, safe, True)
-        return mask[..., : self.k_blocks]
+        return mask[..., : self.k_blocks] | (self.cnt < 0)[..., None]
 
     @staticmethod
     def from_bool_mask(mask: torch.Tensor) -> "BlockLists":

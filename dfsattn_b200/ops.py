@@ -190,8 +190,9 @@ def select_topk(scores, q_rows: int, n_rank: int, k_select: int, dense_row_start
     if scores.dtype != torch.float32 or not scores.is_contiguous():
         raise ValueError("scores must be contiguous fp32")
     H, score_rows, n_cols = scores.shape
-    sparse_cnt = k_select + (n_cols - n_rank)
-    kmax = n_cols if dense_row_start < q_rows else sparse_cnt
+    # lists are as long as a ranked row needs; rows from dense_row_start on get the count -1 ("every key
+    # block") instead of a list of all of them
+    kmax = max(1, k_select + (n_cols - n_rank))
     idx = torch.empty((H, q_rows, kmax), dtype=torch.int32, device=scores.device)
     cnt = torch.empty((H, q_rows), dtype=torch.int32, device=scores.device)
     mask = torch.empty((H, q_rows, n_cols), dtype=torch.uint8, device=scores.device) if want_mask else None

@@ -204,7 +204,10 @@ int dfs_block_scores_static(const void* q_perm, const void* k_perm, int dtype, i
 /* Per (head, row): the k_select largest of scores[h, r, 0:n_rank) (ties: lowest
  * column first), plus every column in [n_rank, n_cols) ("forced" columns),
  * written in ascending order to idx[h, r, 0:cnt) and padded with -1 up to
- * kmax; rows r >= dense_row_start select every column.
+ * kmax (>= k_select + n_cols - n_rank); rows r >= dense_row_start select every
+ * column: listed like the others when kmax >= n_cols, otherwise the row gets
+ * cnt = -1 ("every key block", understood by the attention and counting entry
+ * points) and no list, so that a few dense rows do not set kmax for all rows.
  * Replaces torch.topk + scatter_ and the dense text rules,
  * dfsattn/attention_hyvideo.py:431-443,491-501 and attention_wan.py:248-253.
  * scores: fp32 [H, score_rows, n_cols]; idx: int32 [H, q_rows, kmax];
@@ -224,7 +227,8 @@ int dfs_select_topk(const float* scores, int heads, int score_rows, int q_rows, 
  * with idx == NULL (every key block), flash_attn_varlen_func at
  * dfsattn/fullattention.py:108-116.
  *  q, k, v : bf16 [H, L, D], already permuted; D = 64 or 128.
- *  idx/cnt : int32 [H, Qb, kmax] / [H, Qb] ascending block lists (Qb = ceil(L/128)).
+ *  idx/cnt : int32 [H, Qb, kmax] / [H, Qb] ascending block lists (Qb = ceil(L/128));
+ *            cnt = -1 marks a row that attends every key block (its list is not read).
  *  kv_len  : keys j >= kv_len are masked out (L when there is no padding).
  *  out_row_map : int32 [L] or NULL; row i of the result is stored at row
  *            out_row_map[i] (pass the forward permutation to fuse the

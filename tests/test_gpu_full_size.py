@@ -50,7 +50,8 @@ def test_every_row_selects_its_budget_and_the_pair_count_is_the_references(full)
     cnt = lists.cnt.cpu()
     assert cnt.shape == (HEADS, KB)
     assert bool((cnt[:, :DENSE_START] == K_SEL).all())          # 276 ranked + 3 forced key blocks
-    assert bool((cnt[:, DENSE_START:] == KB).all())             # rows with text tokens are dense
+    assert bool((cnt[:, DENSE_START:] == -1).all())             # rows with text tokens attend every block
+    assert lists.idx.shape[-1] == K_SEL                         # lists as long as a video row needs
     idx = lists.idx[:, :DENSE_START, :K_SEL]
     assert bool((idx[:, :, 1:] > idx[:, :, :-1]).all())         # ascending, no duplicates
     assert bool((idx[:, :, -3:] == torch.arange(DENSE_START, KB, device=idx.device, dtype=idx.dtype)).all())
@@ -126,9 +127,8 @@ def test_kp_tile_maps_at_full_size(full):
     lists = engine.compute_block_lists(qp, kp, VIDEO, SPARSITY, "hyvideo", tile=16, fine_top_p=P)
     assert torch.equal(lists.idx, full["lists"].idx) and lists.fine.shape == lists.idx.shape
     fine = lists.fine
-    assert bool((fine[:, DENSE_START:] == -1).all())                       # dense rows: whole blocks
+    assert lists.fine.shape[-1] == K_SEL                                   # no slots beyond a video row's budget
     assert bool((fine[:, :DENSE_START, K_SEL - 3:K_SEL] == -1).all())      # forced text / boundary columns
-    assert bool((fine[:, :DENSE_START, K_SEL:] == 0).all())                # unused slots
     refined = fine[:, :DENSE_START, :K_SEL - 3]
     assert bool((refined != 0).all())                                      # the largest tile always stays
     shifts = torch.arange(64, device="cuda", dtype=torch.int64)

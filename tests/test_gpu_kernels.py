@@ -79,10 +79,32 @@ def test_select_matches_topk_bit_exact(ops, H, score_rows, q_rows, cols, n_rank,
     want = _select_oracle(scores, n_rank, k, dense, q_rows)
     assert torch.equal(mask.cpu().bool(), want)
     widx, wcnt = oracle.mask_to_index_lists(want)
-    assert torch.equal(cnt.cpu(), wcnt)
+    kmax = idx.shape[-1]
+    assert kmax == max(1, k + cols - n_rank)            # as long as a ranked row needs, not as a dense row
+    idx, cnt = idx.cpu(), cnt.cpu()
+    marked = kmax < cols                                # dense rows then carry the count -1 and no list
+    last_listed = dense if marked else q_rows
+    assert torch.equal(cnt[:, :last_listed], wcnt[:, :last_listed])
+    assert torch.equal(idx[:, :last_listed], widx[:, :last_listed, :kmax])
+    if marked:
+        assert bool((cnt[:, dense:] == -1).all()) and bool((idx[:, dense:] == -1).all())
+    from dfsattn_b200.engine import BlockLists
+    lists = BlockLists(idx.cuda(), cnt.cuda(), cols)
+    assert torch.equal(lists.to_bool_mask().cpu(), want)
+    if q_rows == cols:                                  # the pair count is defined for square masks
+        L = cols * 128 - 37
+        assert ops.interaction_count(lists.idx, lists.cnt, H, L) == oracle.block_interaction_count(want, L)
+    # with room for every column the dense rows are listed like the others
+    from dfsattn_b200 import _lib
+    big = torch.empty((H, q_rows, cols), dtype=torch.int32, device="cuda")
+    bcnt = torch.empty((H, q_rows), dtype=torch.int32, device="cuda")
+    sc = scores.cuda()
+    assert _lib.lib.dfs_select_topk(sc.data_ptr(), H, score_rows, q_rows, cols, n_rank, k, dense, big.data_ptr(),
+                                    bcnt.data_ptr(), cols, None, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(bcnt.cpu(), wcnt)
     kk = widx.shape[-1]
-    assert torch.equal(idx.cpu()[..., :kk], widx)
-    assert (idx.cpu()[..., kk:] == -1).all()
+    assert torch.equal(big.cpu()[..., :kk], widx) and bool((big.cpu()[..., kk:] == -1).all())
 
 
 def test_select_ties_go_to_the_lowest_column(ops):
