@@ -257,8 +257,9 @@ int dfs_block_sparse_fwd_ex(const void* q, const void* k, const void* v, const i
  * slot) it writes a 64-bit map, bit 8 * i + j = the 16 x 16-token tile (query tile i, key tile j)
  * of that 128 x 128 pair is attended: the pair's 64 softmax-ed tile scores are ranked jointly,
  * largest first, and a tile is kept while the scores ranked before it sum to less than fine_top_p
- * times the pair's total (scores exactly equal to the smallest kept one are all kept).  Key blocks >= n_rank (text / boundary columns) and query rows >=
- * dense_row_start keep whole pairs (all ones, :298-301); slots >= cnt get 0.  tile must be 16.
+ * times the pair's total (scores exactly equal to the smallest kept one are all kept).  Key
+ * blocks >= n_rank (text / boundary columns) and query rows >= dense_row_start keep whole pairs (all ones, :298-301; rows with cnt = -1 attend every block
+ * anyway and get 0, their maps are not read); slots >= cnt get 0.  tile must be 16.
  *  idx/cnt   : the lists, int32 [H, q_rows, kmax] / [H, q_rows], each list ascending (as
  *              dfs_select_topk writes them: the refinable entries are then a prefix).
  *  fine_bits : uint64 [H, q_rows, kmax]. */
