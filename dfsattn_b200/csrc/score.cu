@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(256) pool_tiles_kernel(const T* __restrict__ q
 // --------------------------------------------------------------------------
 // pooled logits on tcgen05 + per-block log-sum-exp epilogue
 //
-// One CTA per (128 pooled query rows, head); it walks all 128-column tiles of pooled keys.
+// One CTA per (128 pooled query rows, head, range of key tiles); it walks its 128-column tiles of pooled keys.
 //   warp 0   TMA producer: Q hi/lo once, K hi/lo tiles through a 2-stage ring
 //   warp 1   MMA issuer (one lane): 3 x D/16 MMAs per column tile into one of two TMEM buffers
 //   warps 2-5 epilogue: one thread per pooled query row reads the 128 logits (tcgen05.ld) and
@@ -228,7 +228,13 @@ __global__ void __launch_bounds__(kLseThreads, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y;
   const int row0 = blockIdx.x * kGemmTile;
-  const int n_ct = s.nk_pad / kGemmTile;  // column tiles
+  // Column tiles of this CTA: the key tiles are cut into gridDim.z contiguous ranges (every (query tile,
+  // key block) value is independent of the others, so small head counts still fill the GPU).  `ct`
+  // below counts this CTA's tiles from zero (ring stages and barrier phases); ct0 + ct is the tile.
+  const int ct_total = s.nk_pad / kGemmTile;
+  const int ct_per = (ct_total + static_cast<int>(gridDim.z) - 1) / static_cast<int>(gridDim.z);
+  const int ct0 = static_cast<int>(blockIdx.z) * ct_per;
+  const int n_ct = ct0 >= ct_total ? 0 : (ct_total - ct0 < ct_per ? ct_total - ct0 : ct_per);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -273,7 +279,7 @@ __global__ void __launch_bounds__(kLseThreads, 1)
         for (int part = 0; part < 2; ++part)
           for (int c = 0; c < HD / 64; ++c)
             tma_load_3d(k_ring + (st * 2 + part) * L::kTileBytes + c * L::kBoxBytes, &tm_k, &k_full[st], c * 64,
-                        ct * kGemmTile, 2 * head + part);
+                        (ct0 + ct) * kGemmTile, 2 * head + part);
         ++issued;
       }
       if (!ok) {
@@ -342,7 +348,7 @@ __global__ void __launch_bounds__(kLseThreads, 1)
           float sum = 0.f;
 #pragma unroll
           for (int i = 0; i < TPB; ++i) sum += ex2_approx(v[i] - m);
-          const int kb = ct * (kGemmTile / TPB) + g * (32 / TPB) + grp;
+          const int kb = (ct0 + ct) * (kGemmTile / TPB) + g * (32 / TPB) + grp;
           if (row < s.nq && kb < s.k_blocks) out_row[kb] = m + lg2_approx(sum);
         }
       }
@@ -417,7 +423,12 @@ int launch_lse(const __nv_bfloat16* qm, const __nv_bfloat16* km, float* lse, con
   if (rc != 0) return rc;
   DFS_CUDA_CHECK(
       cudaFuncSetAttribute(tile_lse_kernel<HD, TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-  dim3 grid(s.nq_pad / kGemmTile, s.heads);
+  // at least ~4 CTAs per SM's worth of work items: split the key tiles when heads x query tiles are few
+  const int ctas = (s.nq_pad / kGemmTile) * s.heads, ct_total = s.nk_pad / kGemmTile;
+  int splits = (4 * 148 + ctas - 1) / ctas;
+  splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
+  if (splits > ct_total) splits = ct_total;
+  dim3 grid(s.nq_pad / kGemmTile, s.heads, splits);
   tile_lse_kernel<HD, TPB><<<grid, kLseThreads, L::kTotal, stream>>>(mq, mk, lse, s, scale_log2, status);
   return static_cast<int>(cudaGetLastError());
 }

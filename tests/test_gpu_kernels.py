@@ -205,3 +205,23 @@ def test_block_scores_rejects_bad_shapes(ops):
         ops.block_scores(x, x, 129, False)  # [video | gap | text] does not fit in Kb blocks
     with pytest.raises(ValueError):
         ops.block_scores(x.half(), x.half(), 256, True)
+
+
+@pytest.mark.parametrize("heads,text", [(1, 0), (2, 200)])
+def test_block_scores_few_heads_long_sequence(ops, heads, text):
+    """Few heads and thousands of key tiles: the logits kernel then cuts the key tiles into several
+    ranges per (query tile, head); every range must land in its own columns."""
+    from dfsattn_b200.synthetic import structured_qkv
+    grid = (5, 16, 64)                                          # 5 120 video tokens: 40 key blocks, 3 column tiles
+    q, k, _ = structured_qkv(grid, heads, 128, text_len=text, dtype=torch.float32, device="cpu", seed=3)
+    L = q.shape[2]
+    video_len = L - text
+    perm = torch.randperm(video_len, generator=torch.Generator().manual_seed(1))
+    perm = torch.cat([perm, torch.arange(video_len, L)])
+    qp, kp = q[0][:, perm].contiguous().cuda(), k[0][:, perm].contiguous().cuda()
+    for wan in ((True,) if text == 0 else (False,)):
+        got = ops.block_scores(qp, kp, L if wan else video_len, wan).cpu()
+        want = (oracle.block_scores_wan(q, k, perm) if wan else oracle.block_scores_hyvideo(q, k, perm, video_len))[0]
+        torch.testing.assert_close(got, want, rtol=2e-4, atol=1e-6)
+    torch.cuda.synchronize()
+    ops.check_status("cuda")
