@@ -157,13 +157,51 @@ def dist_env():
 
 
 # --------------------------------------------------------------------------- #
-# CPU reference arm / cpu_baseline: the oracle restatement on the host cores
+# CPU reference arm / cpu_baseline: the reference's path on the host cores
 # --------------------------------------------------------------------------- #
-def cpu_sample(spec, budget_blocks):
-    """One bounded sample of the workload on the CPU: ONE head, full scoring and
-    selection, attention for `budget_blocks` query blocks.  Returns (flops, s, note)."""
+def load_by_path(name, path):
+    """Import one source file without importing the package around it (the reference arm must
+    not map libdfs_b200.so, which `import dfsattn_b200` does)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def host_threads():
+    """Use every core this process may run on (torch.distributed.run exports OMP_NUM_THREADS=1)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
+def reference_modules():
+    """The reference's own attention modules when a checkout is reachable: the directory named by
+    DFSATTN_REFERENCE_PATH, else baseline/_ref (not part of the source tree).  (None, reason) otherwise."""
+    for cand in (os.environ.get("DFSATTN_REFERENCE_PATH"), os.path.join(ROOT, "baseline", "_ref")):
+        if cand and os.path.exists(os.path.join(cand, "dfsattn", "attention_hyvideo.py")):
+            try:
+                if cand not in sys.path:
+                    sys.path.insert(0, cand)
+                import dfsattn.attention_hyvideo as ref_hy
+                import dfsattn.attention_wan as ref_wan
+                return (ref_hy, ref_wan), cand
+            except Exception as exc:  # noqa: BLE001  (any import problem means: use the port)
+                return None, f"reference at {cand} does not import: {type(exc).__name__}: {exc}"
+    return None, "no reference checkout reachable"
+
+
+def cpu_sample(spec, budget_blocks, ref=None):
+    """One bounded sample of the workload on the CPU: ONE head, full scoring and selection,
+    attention for the first `budget_blocks` query blocks.  With `ref` (the reference's own modules)
+    the reference's `_compute_block_mask` and its packed CPU attention loop do the work, else the
+    oracle restatement of the same two functions.  Returns (flops, seconds, note)."""
     import oracle
-    from dfsattn_b200.synthetic import structured_qkv
+    structured_qkv = load_by_path("_dfs_synthetic", os.path.join(ROOT, "dfsattn_b200", "synthetic.py")).structured_qkv
     torch.manual_seed(0)
     f, h, w = spec["grid"]
     q, k, v = structured_qkv(spec["grid"], 1, spec["dim"], text_len=spec["text"], dtype=torch.float32,
@@ -172,17 +210,30 @@ def cpu_sample(spec, budget_blocks):
     video_len = L - spec["text"]
     vperm = torch.from_numpy(oracle.hilbert3d_perm(f, h, w)) if spec.get("order", "hilbert3d") == "hilbert3d" \
         else None
-    perm, inv = oracle.build_permutation(vperm, L, video_len)
-    t0 = time.perf_counter()
-    if spec["flavor"] == "hyvideo":
-        mask = oracle.block_mask_hyvideo(q, k, perm, video_len, spec["sparsity"])
+    hy = spec["flavor"] == "hyvideo"
+    if ref is not None:
+        ref_hy, ref_wan = ref
+        attn = ref_hy.DFS_Attention(0, 0, spec["sparsity"], True, video_len, vperm, 128, 16, 16)
+        scorer = attn if hy else ref_wan.DFS_Attention(0, 0, spec["sparsity"], True, vperm, 128, 16, 16)
+        perm, inv = attn._compute_permutation(vperm, L, torch.device("cpu"))
+        t0 = time.perf_counter()
+        mask = scorer._compute_block_mask(q, k, perm, spec["sparsity"])
+        t_mask = time.perf_counter() - t0
     else:
-        mask = oracle.block_mask_wan(q, k, perm, spec["sparsity"])
-    t_mask = time.perf_counter() - t0
+        perm, inv = oracle.build_permutation(vperm, L, video_len)
+        t0 = time.perf_counter()
+        mask = (oracle.block_mask_hyvideo(q, k, perm, video_len, spec["sparsity"]) if hy
+                else oracle.block_mask_wan(q, k, perm, spec["sparsity"]))
+        t_mask = time.perf_counter() - t0
     qb_total = mask.shape[1]
     nb = min(budget_blocks, qb_total)
     t0 = time.perf_counter()
-    oracle.block_sparse_attention(q, k, v, perm, inv, mask, q_block_range=(0, nb))
+    if ref is not None:
+        # the reference's loop walks the rows of the mask it is given: the first nb query blocks
+        sub_mask = mask[:, :nb].contiguous()
+        attn._run_oracle_hybrid_attention(q, k, v, perm, inv, sub_mask, torch.zeros_like(sub_mask))
+    else:
+        oracle.block_sparse_attention(q, k, v, perm, inv, mask, q_block_range=(0, nb))
     t_attn = time.perf_counter() - t0
     sub = mask[:, :nb].clone()
     rows = min(nb * 128, L)
@@ -193,29 +244,48 @@ def cpu_sample(spec, budget_blocks):
     flops = 4.0 * spec["dim"] * pairs
     # scoring is per call for the whole head: charge the share of the sampled rows
     seconds = t_attn + t_mask * (nb / qb_total)
-    note = (f"1 of {spec['heads']} heads; scoring+selection of the whole head ({t_mask:.2f} s, charged "
-            f"{nb}/{qb_total}) + attention of query blocks 0..{nb - 1} ({rows} rows, {t_attn:.2f} s)")
+    who = "the reference's own _compute_block_mask + packed CPU attention loop" if ref is not None \
+        else "oracle port of the reference's _compute_block_mask + packed CPU attention loop"
+    note = (f"{who}, fp32; 1 of {spec['heads']} heads; scoring+selection of the whole head ({t_mask:.2f} s, "
+            f"charged {nb}/{qb_total}) + attention of query blocks 0..{nb - 1} ({rows} rows, {t_attn:.2f} s)")
     return flops, seconds, note
 
 
+def workload_config(args, spec, world):
+    """The `config` object both arms print (same keys, same values)."""
+    f, h, w = spec["grid"]
+    L = f * h * w + spec["text"]
+    return {"workload": args.workload, "grid": list(spec["grid"]), "text_tokens": spec["text"], "seq_len": L,
+            "heads": spec["heads"], "heads_per_gpu": spec["heads"] // max(world, 1), "head_dim": spec["dim"],
+            "sparsity": spec["sparsity"], "order": spec.get("order", "hilbert3d"), "block": 128, "tile": 16,
+            "step": "refresh call: permute + score + select + attention (+fused unpermute)"}
+
+
 def run_reference(args, spec, rank, world):
+    """The reference arm: the reference's CPU implementation of the path on the host cores, rank 0
+    only, with every core the process may use.  Nothing of the product is imported."""
     if rank != 0:
         return
-    cores = torch.get_num_threads()
+    cores = host_threads()
+    ref, where = reference_modules()
     times, flops_list, note = [], [], ""
     for i in range(args.warmup + args.steps):
-        fl, s, note = cpu_sample(spec, args.cpu_blocks)
+        fl, s, note = cpu_sample(spec, args.cpu_blocks, ref)
         if i >= args.warmup:
             times.append(s)
             flops_list.append(fl)
     value = sum(flops_list) / sum(times) / 1e12
+    kind = "reference" if ref is not None else "port"
+    config = workload_config(args, spec, args.gpus)
+    config["parallelism"] = f"host cores of rank 0 ({cores} threads); the GPU arm's heads are sharded x{args.gpus}"
+    config["sample"] = note
+    config["reference_source"] = where
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "note": "CPU oracle port of the reference path (the reference "
-                   "is Python and needs packages absent offline); each step is a bounded sample"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": note},
+        "config": config,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": note},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -252,156 +322,387 @@ def quartiles(xs):
     return {"median": at(0.5), "p25": at(0.25), "p75": at(0.75)}
 
 
-def run_trace(args, spec, rank, local_rank, world):
-    """The mask-caching trace on the GPU: per denoising step and layer either the dense call (warm-up
-    steps), a refresh call (score + select + attention) or a call on cached lists, Q and K drifting
-    from step to step (x <- 0.98 x + 0.2 N(0,1), outside the timed intervals).  One bench step is the
-    whole 50-step trace; the time is the sum of the CUDA-event intervals around the attention calls."""
-    import torch.distributed as dist
+class Ranks:
+    """The process group of a run (one process per GPU) and the two reductions the bench needs."""
+
+    def __init__(self, rank, local_rank, world):
+        import torch.distributed as dist
+        self.dist, self.rank, self.world = dist, rank, world
+        torch.cuda.set_device(local_rank)
+        self.dev = torch.device("cuda", local_rank)
+        if world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+
+    def _reduce(self, x, op):
+        if self.world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=self.dev)
+        self.dist.all_reduce(t, op=op)
+        return float(t.item())
+
+    def max(self, x):
+        return self._reduce(x, self.dist.ReduceOp.MAX)
+
+    def sum(self, x):
+        return self._reduce(x, self.dist.ReduceOp.SUM)
+
+    def min(self, x):
+        return self._reduce(x, self.dist.ReduceOp.MIN)
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
+def operator_call(spec, vperm, video_len, layer_idx=0):
+    """The refresh call of the operator for a workload: step 12 (24 for Wan's doubled counter) is a
+    refresh step, so scoring and selection run on every call."""
+    from dfsattn_b200.attention_hyvideo import dfs_attention as hy_attention
+    from dfsattn_b200.attention_wan import dfs_attention as wan_attention
+    common = dict(skip_steps=12, cache_interval=12, layer_idx=layer_idx, sparsity=spec["sparsity"],
+                  sparsity_dcrt=0.1, tile_size=16, block_size=128, video_perm=vperm)
+    if spec["flavor"] == "hyvideo":
+        return lambda qq, kk, vv, **extra: hy_attention(qq, kk, vv, step_idx=12, video_len=video_len, **common,
+                                                        **extra)
+    return lambda qq, kk, vv, **extra: wan_attention(qq, kk, vv, step_idx=24, **common, **extra)
+
+
+def attention_class(spec):
+    from dfsattn_b200.attention_hyvideo import DFS_Attention as HyAttn
+    from dfsattn_b200.attention_wan import DFS_Attention as WanAttn
+    return HyAttn if spec["flavor"] == "hyvideo" else WanAttn
+
+
+def cached_pairs(spec, h_local, L):
+    """Attended token pairs of this rank's heads, from the lists the last refresh call cached."""
     from dfsattn_b200 import ops
+    lists = next(iter(attention_class(spec)._cached_metadata.values()))["block_lists"]
+    return ops.interaction_count(lists.idx, lists.cnt, h_local, L), lists
+
+
+# ---- the mask-caching trace --------------------------------------------------
+def trace_pass(rk, spec, base, vperm, layout):
+    """One 50-step trace over the layers in `base` (per layer q, k, v: head shards [1, H/P, L, D], or
+    with layout "seq" sequence shards [1, H, L_r, D] swapped by NCCL all-to-alls around every call):
+    per denoising step and layer either the dense call (warm-up steps), a refresh call (score +
+    select + attention) or a call on cached lists, Q and K drifting from step to step
+    (x <- 0.98 x + 0.2 N(0,1), outside the timed intervals).  Returns [(kind, sparsity, ms)]."""
+    from dfsattn_b200 import parallel
     from dfsattn_b200.attention_hyvideo import (DFS_Attention, _compute_cache_schedule, _dfs_attention_instances,
                                                 dfs_attention)
     from dfsattn_b200.fullattention import full_attention
-    from dfsattn_b200.order import hilbert3d_perm
-    from dfsattn_b200.synthetic import drift, structured_qkv
-
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    H, D = spec["heads"], spec["dim"]
-    if H % world != 0:
-        raise SystemExit(f"{H} heads do not split over {world} ranks")
-    h_local = H // world
-    layers, n_steps, skip, interval, s0, dcrt = args.trace_layers, 50, 12, 12, spec["sparsity"], 0.1
-    vperm = hilbert3d_perm(*spec["grid"])
-    base = [structured_qkv(spec["grid"], h_local, D, text_len=spec["text"], dtype=torch.bfloat16, device=dev,
-                           seed=layer, head_offset=rank * h_local, total_heads=H) for layer in range(layers)]
-    L = base[0][0].shape[2]
+    from dfsattn_b200.synthetic import drift
+    n_steps, skip, interval, s0, dcrt = 50, 12, 12, spec["sparsity"], 0.1
+    L = spec["grid"][0] * spec["grid"][1] * spec["grid"][2] + spec["text"]
     video_len = L - spec["text"]
+    DFS_Attention.clear_cache()
+    _dfs_attention_instances.clear()
+    state = [list(t) for t in base]
+    spans = []
+    for step in range(n_steps):
+        flag, cur = _compute_cache_schedule(step, skip, interval, s0, dcrt)
+        for layer in range(len(base)):
+            q, k, v = state[layer]
+            if step > 0:
+                q = drift(q, 1000 * layer + step)
+                k = drift(k, 500000 + 1000 * layer + step)
+                state[layer][0], state[layer][1] = q, k
+            if step < skip:
+                fn = lambda a, b, c: full_attention(a, b, c, mode="flash")  # noqa: E731
+                kind = "dense"
+            else:
+                fn = lambda a, b, c: dfs_attention(  # noqa: E731
+                    a, b, c, step_idx=step, skip_steps=skip, cache_interval=interval, layer_idx=layer,
+                    sparsity=s0, sparsity_dcrt=dcrt, tile_size=16, block_size=128, video_len=video_len,
+                    video_perm=vperm)
+                kind = "refresh" if flag else "cached"
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            if layout == "seq":
+                parallel.dfs_attention_sequence_parallel(q, k, v, L, fn)
+            else:
+                fn(q, k, v)
+            e1.record()
+            spans.append((kind, round(cur, 6), e0, e1))
+    torch.cuda.synchronize()
+    return [(kind, s, e0.elapsed_time(e1)) for kind, s, e0, e1 in spans]
 
-    def one_trace():
-        DFS_Attention.clear_cache()
-        _dfs_attention_instances.clear()
-        state = [list(t) for t in base]
-        spans = []   # (kind, sparsity, start event, end event)
-        for step in range(n_steps):
-            flag, cur = _compute_cache_schedule(step, skip, interval, s0, dcrt)
-            for layer in range(layers):
-                q, k, v = state[layer]
-                if step > 0:
-                    q = drift(q, 1000 * layer + step)
-                    k = drift(k, 500000 + 1000 * layer + step)
-                    state[layer][0], state[layer][1] = q, k
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                if step < skip:
-                    full_attention(q, k, v, mode="flash")
-                    kind = "dense"
-                else:
-                    dfs_attention(q, k, v, step_idx=step, skip_steps=skip, cache_interval=interval, layer_idx=layer,
-                                  sparsity=s0, sparsity_dcrt=dcrt, tile_size=16, block_size=128,
-                                  video_len=video_len, video_perm=vperm)
-                    kind = "refresh" if flag else "cached"
-                e1.record()
-                spans.append((kind, round(cur, 6), e0, e1))
-        torch.cuda.synchronize()
-        return spans
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
+def trace_inputs(rk, spec, layers, layout):
+    from dfsattn_b200 import parallel
+    from dfsattn_b200.synthetic import structured_qkv
+    H, D = spec["heads"], spec["dim"]
+    h_local = H // rk.world
+    base = []
+    for layer in range(layers):
+        if layout == "seq":
+            full = structured_qkv(spec["grid"], H, D, text_len=spec["text"], dtype=torch.bfloat16, device=rk.dev,
+                                  seed=layer)
+            t0, tn = parallel.seq_shard(full[0].shape[2], rk.rank, rk.world)
+            base.append(tuple(t[:, :, t0:t0 + tn].contiguous() for t in full))
+            del full
+        else:
+            base.append(structured_qkv(spec["grid"], h_local, D, text_len=spec["text"], dtype=torch.bfloat16,
+                                       device=rk.dev, seed=layer, head_offset=rk.rank * h_local, total_heads=H))
+    return base
 
-    for _ in range(args.warmup):
-        one_trace()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    barrier()
-    totals, per_kind = [], {}
-    for _ in range(args.steps):
-        spans = one_trace()
-        ms = [(kind, s, e0.elapsed_time(e1)) for kind, s, e0, e1 in spans]
-        totals.append(sum(t for _, _, t in ms))
-        for kind, s, t in ms:
-            key = kind if kind == "dense" else f"{kind}@{s:g}"
-            per_kind.setdefault(key, []).append(t)
-    barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    ops.check_status(dev)
-    # algorithmic FLOPs of one trace: dense calls 4*D*L^2 per head, sparse calls 4*D*pairs of their lists
+
+def trace_flops(spec, layers, h_local, L):
+    """Algorithmic FLOPs of one trace on this rank: dense calls 4*D*L^2 per head, sparse calls
+    4*D*pairs of the lists they ran on (read back from the cache the trace left behind)."""
+    from dfsattn_b200 import ops
+    from dfsattn_b200.attention_hyvideo import DFS_Attention, _compute_cache_schedule
     pairs = {}
     for key, entry in DFS_Attention._cached_metadata.items():
         lists = entry["block_lists"]
         pairs[(key[0], round(key[4], 6))] = ops.interaction_count(lists.idx, lists.cnt, h_local, L)
     flops = 0.0
-    for step in range(n_steps):
-        _, cur = _compute_cache_schedule(step, skip, interval, s0, dcrt)
+    for step in range(50):
+        _, cur = _compute_cache_schedule(step, 12, 12, spec["sparsity"], 0.1)
         for layer in range(layers):
-            flops += 4.0 * D * (h_local * L * L if step < skip else pairs[(layer, round(cur, 6))])
-    secs = sum(totals) / len(totals) / 1e3
-    if world > 1:
-        t = torch.tensor([secs, flops], dtype=torch.float64, device=dev)
-        mx = t.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        secs, flops = float(mx[0]), float(t[1])
+            flops += 4.0 * spec["dim"] * (h_local * L * L if step < 12 else pairs[(layer, round(cur, 6))])
+    return flops
+
+
+def summarize_trace(rk, spec, layers, runs, L):
+    """(seconds per trace: max over ranks, FLOPs per trace: all ranks, per-kind table)."""
+    h_local = spec["heads"] // rk.world
+    totals, per_kind = [], {}
+    for ms in runs:
+        totals.append(sum(t for _, _, t in ms))
+        for kind, s, t in ms:
+            per_kind.setdefault(kind if kind == "dense" else f"{kind}@{s:g}", []).append(t)
+    secs = rk.max(sum(totals) / len(totals) / 1e3)
+    flops = rk.sum(trace_flops(spec, layers, h_local, L))
+    table = {k: {"calls_per_trace": len(v) // len(runs), "mean_ms": rk.max(sum(v) / len(v))}
+             for k, v in sorted(per_kind.items())}
+    return secs, flops, table
+
+
+def run_trace(args, spec, rank, local_rank, world):
+    """Workloads *_trace: one bench step is the whole 50-step trace; the time is the sum of the
+    CUDA-event intervals around the attention calls (max over ranks)."""
+    from dfsattn_b200 import ops
+    from dfsattn_b200.order import hilbert3d_perm
+    rk = Ranks(rank, local_rank, world)
+    H, D = spec["heads"], spec["dim"]
+    if H % world != 0:
+        raise SystemExit(f"{H} heads do not split over {world} ranks")
+    layout = "seq" if args.layout == "seq" and world > 1 else "head"
+    if args.layout == "seq-fused":
+        raise SystemExit("the trace runs head-sharded (--layout head) or with NCCL all-to-alls (--layout seq)")
+    layers = args.trace_layers
+    vperm = hilbert3d_perm(*spec["grid"])
+    base = trace_inputs(rk, spec, layers, layout)
+    L = spec["grid"][0] * spec["grid"][1] * spec["grid"][2] + spec["text"]
+    for _ in range(args.warmup):
+        trace_pass(rk, spec, base, vperm, layout)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    rk.barrier()
+    runs = [trace_pass(rk, spec, base, vperm, layout) for _ in range(args.steps)]
+    rk.barrier()
+    clocks = sampler.stop()
+    ops.check_status(rk.dev)
+    secs, flops, table = summarize_trace(rk, spec, layers, runs, L)
+    cycles = rk.max(1e3 * secs * (clocks["sm_mhz"] or 0.0))
     if rank == 0:
         pk = peaks()
         value = flops / secs / 1e12
+        config = workload_config(args, spec, world)
+        config.update({"layers": layers, "denoising_steps": 50,
+                       "schedule": {"skip_steps": 12, "cache_interval": 12, "sparsity": spec["sparsity"],
+                                    "sparsity_dcrt": 0.1},
+                       "step": "one 50-step trace: dense warm-up calls, refresh calls, calls on cached lists",
+                       "parallelism": (f"sequence-sharded x{world}: NCCL all-to-all in and out around every call"
+                                       if layout == "seq" else f"head-sharded x{world}, no collective"),
+                       "l2": "inputs larger than L2 (no flush needed)", "flops_per_trace": flops})
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": 1e3 * secs, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "grid": list(spec["grid"]), "text_tokens": spec["text"],
-                       "seq_len": L, "heads": H, "heads_per_gpu": h_local, "head_dim": D, "layers": layers,
-                       "denoising_steps": n_steps, "schedule": {"skip_steps": skip, "cache_interval": interval,
-                                                                "sparsity": s0, "sparsity_dcrt": dcrt},
-                       "step": "one 50-step trace: dense warm-up calls, refresh calls, calls on cached lists",
-                       "parallelism": f"head-sharded x{world}, no collective",
-                       "l2": "inputs larger than L2 (no flush needed)", "flops_per_trace": flops},
+            "warmup": args.warmup, "ms_per_step": 1e3 * secs, "ms_x_mhz": cycles, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
             "clocks": clocks,
-            # dense call: the attention kernel; cached: permute + attention; refresh: + pool, tile LSE,
-            # block sums and selection
-            "gpu_launches": sum(len(v) * (1 if k == "dense" else 6 if k.startswith("refresh") else 2)
-                                for k, v in per_kind.items()),
-            "calls_ms": {k: {"calls_per_trace": len(v) // args.steps, "mean_ms": sum(v) / len(v)}
-                         for k, v in sorted(per_kind.items())},
-            "roofline": {"bound": "tensor", "kernel": "bsattn_fwd_kernel<128>", "achieved": value,
+            # dense call: the attention kernel; cached: permute + attention; refresh: + pool, tile scores,
+            # normalisers and selection
+            "gpu_launches": args.steps * sum(v["calls_per_trace"] * (1 if k == "dense" else 6 if
+                                             k.startswith("refresh") else 2) for k, v in table.items()),
+            "calls_ms": table,
+            "roofline": {"bound": "tensor", "kernel": "bsattn_fwd_kernel<128>", "achieved": value / world,
                          "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                         "frac": value / pk["bf16_tflops_sustained"],
+                         "frac": value / world / pk["bf16_tflops_sustained"],
                          "peak_source": f"{pk['source']} sustained cuBLAS bf16", "traffic": None},
             "e2e": None, "cpu_baseline": None,
         }
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    rk.close()
+
+
+# ---- the other configurations, one timed call each ------------------------------
+def other_configs(rk, args):
+    """One timed refresh call each of the Wan shapes (480p; 720p at three sparsities and in raster
+    order) and one 50-step, 1-layer mask-caching trace of the HunyuanVideo 720p shape, all sharded
+    over the ranks of this run by head; at N > 1 the trace also with sequence-sharded inputs."""
+    from dfsattn_b200.order import hilbert3d_perm
+    from dfsattn_b200.synthetic import structured_qkv
+    out = {}
+    cases = [("wan_480p", 0.3, "hilbert3d"), ("wan_720p", 0.1, "hilbert3d"), ("wan_720p", 0.3, "hilbert3d"),
+             ("wan_720p", 0.5, "hilbert3d"), ("wan_720p", 0.3, "org")]
+    held = (None, None)
+    for name, sparsity, order in cases:
+        spec = dict(WORKLOADS[name], sparsity=sparsity, order=order)
+        H, D = spec["heads"], spec["dim"]
+        if H % rk.world:
+            continue
+        h_local = H // rk.world
+        if held[0] != name:
+            held = (None, None)
+            held = (name, structured_qkv(spec["grid"], h_local, D, dtype=torch.bfloat16, device=rk.dev, seed=0,
+                                         head_offset=rk.rank * h_local, total_heads=H))
+        q, k, v = held[1]
+        L = q.shape[2]
+        vperm = hilbert3d_perm(*spec["grid"]) if order == "hilbert3d" else None
+        call = operator_call(spec, vperm, L, layer_idx=("cfg", name, sparsity, order))
+        attention_class(spec).clear_cache()
+        secs = rk.max(timed(lambda: call(q, k, v), 3, rk.barrier, warm=2) / 3)
+        pairs, _ = cached_pairs(spec, h_local, L)
+        flops = rk.sum(4.0 * D * pairs)
+        out[f"{name}_s{sparsity:g}_{'hilbert3d' if order == 'hilbert3d' else 'raster'}"] = {
+            "ms_per_call": 1e3 * secs, "tflops": flops / secs / 1e12, "heads_per_gpu": h_local, "seq_len": L}
+        attention_class(spec).clear_cache()
+    del held
+    spec = dict(WORKLOADS["hunyuan_720p_trace"], order="hilbert3d")
+    if spec["heads"] % rk.world == 0:
+        vperm = hilbert3d_perm(*spec["grid"])
+        L = spec["grid"][0] * spec["grid"][1] * spec["grid"][2] + spec["text"]
+        for layout in (["head", "seq"] if rk.world > 1 else ["head"]):
+            base = trace_inputs(rk, spec, 1, layout)
+            rk.barrier()
+            run = trace_pass(rk, spec, base, vperm, layout)
+            secs, flops, table = summarize_trace(rk, spec, 1, [run], L)
+            out[f"hunyuan_720p_trace_1layer_{layout}"] = {
+                "ms_per_trace": 1e3 * secs, "tflops": flops / secs / 1e12,
+                "calls_ms": {k: round(v["mean_ms"], 3) for k, v in table.items()}}
+            del base
+        attention_class(spec).clear_cache()
+    return out
+
+
+# ---- sequence-sharded inputs (N > 1) ----------------------------------------------
+def sequence_layouts(rk, spec, vperm, flops_total):
+    """The step with inputs that arrive sequence-sharded, both forms: NCCL all-to-alls around the
+    head-sharded call, and the fused exchange (peer loads in the gather, peer stores in the attention
+    epilogue); the two all-to-alls alone; and on a small case whether both forms give the bits of
+    the single-GPU call."""
+    from dfsattn_b200 import engine, parallel
+    from dfsattn_b200.attention_hyvideo import DFS_Attention, _dfs_attention_instances, dfs_attention
+    from dfsattn_b200.order import hilbert3d_perm
+    from dfsattn_b200.synthetic import structured_qkv
+    H, D = spec["heads"], spec["dim"]
+    full = structured_qkv(spec["grid"], H, D, text_len=spec["text"], dtype=torch.bfloat16, device=rk.dev, seed=0)
+    L = full[0].shape[2]
+    video_len = L - spec["text"]
+    t0, tn = parallel.seq_shard(L, rk.rank, rk.world)
+    shards = tuple(t[:, :, t0:t0 + tn].contiguous() for t in full)
+    del full
+    head_call = operator_call(spec, vperm, video_len, layer_idx=("seq",))
+    out = {}
+    secs = timed(lambda: parallel.dfs_attention_sequence_parallel(*shards, L, head_call), 3, rk.barrier, warm=2) / 3
+    out["seq_ms"] = 1e3 * rk.max(secs)
+
+    def swaps_only():
+        heads = parallel.seq_to_head_shards([t[0] for t in shards], L)
+        parallel.head_to_seq_shards(heads[0], H)
+    out["all_to_all_ms"] = 1e3 * rk.max(timed(swaps_only, 3, rk.barrier, warm=1) / 3)
+    exchange = parallel.SequenceShardExchange(H, L, D, rk.dev)
+    for dst, src in zip(exchange.inputs(), shards):
+        dst.copy_(src[0])
+    perm_dev, _ = engine._perm_cache.get(vperm, L, video_len, rk.dev)
+    secs = timed(lambda: exchange.run(head_call, perm_dev), 3, rk.barrier, warm=2) / 3
+    out["seq_fused_ms"] = 1e3 * rk.max(secs)
+    out["seq_tflops"] = flops_total / (out["seq_ms"] / 1e3) / 1e12
+    out["seq_fused_tflops"] = flops_total / (out["seq_fused_ms"] / 1e3) / 1e12
+    del exchange, shards
+
+    # parity on a small case (L = 1360: neither a multiple of the world size nor of 128)
+    grid, text, Hs = (5, 12, 21), 100, 8
+    q, k, v = structured_qkv(grid, Hs, D, text_len=text, dtype=torch.bfloat16, device=rk.dev, seed=0)
+    Ls = q.shape[2]
+    sperm = hilbert3d_perm(*grid)
+    kw = dict(step_idx=12, skip_steps=12, cache_interval=12, sparsity=0.5, sparsity_dcrt=0.1, tile_size=16,
+              block_size=128, video_len=Ls - text, video_perm=sperm, layer_idx=("seq-parity",))
+
+    def reset():
+        DFS_Attention.clear_cache()
+        _dfs_attention_instances.clear()
+    s0, sn = parallel.seq_shard(Ls, rk.rank, rk.world)
+    small = [t[:, :, s0:s0 + sn].contiguous() for t in (q, k, v)]
+    reset()
+    whole = dfs_attention(q, k, v, **kw)[0, :, s0:s0 + sn]
+    reset()
+    swapped = parallel.dfs_attention_sequence_parallel(*small, Ls, lambda a, b, c: dfs_attention(a, b, c, **kw))[0]
+    reset()
+    ex = parallel.SequenceShardExchange(Hs, Ls, D, rk.dev)
+    for dst, src in zip(ex.inputs(), small):
+        dst.copy_(src[0])
+    sperm_dev, _ = engine._perm_cache.get(sperm, Ls, Ls - text, rk.dev)
+    fused = ex.run(lambda a, b, c, **e: dfs_attention(a, b, c, **kw, **e), sperm_dev).clone()
+    torch.cuda.synchronize()
+    same = float(torch.equal(swapped, whole) and torch.equal(fused, whole))
+    out["seq_parity"] = bool(rk.min(same) == 1.0)
+    reset()
+    return out
+
+
+def copy_rates(rk, host_in, host_out, dev_in, dev_out):
+    """Host<->device copy rates of this step's buffers with every rank copying at the same time:
+    uploads alone, downloads alone, and both directions together on two streams (the floor of the
+    host-buffer call: nothing of it can end before its bytes have crossed)."""
+    up_s, down_s = torch.cuda.Stream(rk.dev), torch.cuda.Stream(rk.dev)
+    cur = torch.cuda.current_stream(rk.dev)
+
+    def up():
+        up_s.wait_stream(cur)
+        with torch.cuda.stream(up_s):
+            for d, h in zip(dev_in, host_in):
+                d.copy_(h, non_blocking=True)
+        cur.wait_stream(up_s)
+
+    def down():
+        down_s.wait_stream(cur)
+        with torch.cuda.stream(down_s):
+            host_out.copy_(dev_out, non_blocking=True)
+        cur.wait_stream(down_s)
+
+    def both():
+        up_s.wait_stream(cur)
+        down_s.wait_stream(cur)
+        with torch.cuda.stream(up_s):
+            for d, h in zip(dev_in, host_in):
+                d.copy_(h, non_blocking=True)
+        with torch.cuda.stream(down_s):
+            host_out.copy_(dev_out, non_blocking=True)
+        cur.wait_stream(up_s)
+        cur.wait_stream(down_s)
+    up_bytes = sum(h.numel() * h.element_size() for h in host_in)
+    down_bytes = host_out.numel() * host_out.element_size()
+    t_up = rk.max(timed(up, 3, rk.barrier, warm=1) / 3)
+    t_down = rk.max(timed(down, 3, rk.barrier, warm=1) / 3)
+    t_both = rk.max(timed(both, 3, rk.barrier, warm=1) / 3)
+    return {"h2d_gbs_per_gpu": up_bytes / t_up / 1e9, "d2h_gbs_per_gpu": down_bytes / t_down / 1e9,
+            "copy_only_ms": 1e3 * t_both}
 
 
 def run_gpu(args, spec, rank, local_rank, world):
-    import torch.distributed as dist
     from dfsattn_b200 import engine, ops
-    from dfsattn_b200.attention_hyvideo import DFS_Attention as HyAttn, dfs_attention as hy_attention
-    from dfsattn_b200.attention_wan import DFS_Attention as WanAttn, dfs_attention as wan_attention
     from dfsattn_b200.order import hilbert3d_perm
     from dfsattn_b200.synthetic import structured_qkv
 
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-
-    def reduce(x, op):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=op)
-        return float(t.item())
-
+    rk = Ranks(rank, local_rank, world)
+    dev, barrier = rk.dev, rk.barrier
     H, D = spec["heads"], spec["dim"]
     if H % world != 0:
         raise SystemExit(f"{H} heads do not split over {world} ranks")
@@ -427,17 +728,8 @@ def run_gpu(args, spec, rank, local_rank, world):
     video_len = L - spec["text"]
     vperm = hilbert3d_perm(f, h, w) if spec.get("order", "hilbert3d") == "hilbert3d" else None
     hy = spec["flavor"] == "hyvideo"
-    Attn = HyAttn if hy else WanAttn
-
-    def call(qq, kk, vv, **extra):
-        # step 12 (24 for Wan's doubled counter) is a refresh step: score + select run every call
-        if hy:
-            return hy_attention(qq, kk, vv, step_idx=12, skip_steps=12, cache_interval=12, layer_idx=0,
-                                sparsity=spec["sparsity"], sparsity_dcrt=0.1, tile_size=16, block_size=128,
-                                video_len=video_len, video_perm=vperm, **extra)
-        return wan_attention(qq, kk, vv, step_idx=24, skip_steps=12, cache_interval=12, layer_idx=0,
-                             sparsity=spec["sparsity"], sparsity_dcrt=0.1, tile_size=16, block_size=128,
-                             video_perm=vperm, **extra)
+    Attn = attention_class(spec)
+    call = operator_call(spec, vperm, video_len)
 
     if fused_exchange:
         # shards in symmetric memory; the gather reads peers, the attention epilogue writes peers
@@ -464,17 +756,18 @@ def run_gpu(args, spec, rank, local_rank, world):
         out = call(*step_inputs)
     torch.cuda.synchronize()
     ops.check_status(dev)
-    lists = next(iter(Attn._cached_metadata.values()))["block_lists"]
-    pairs_local = ops.interaction_count(lists.idx, lists.cnt, h_local, L)
-    flops_total = reduce(4.0 * D * pairs_local, dist.ReduceOp.SUM if world > 1 else None)
+    pairs_local, lists = cached_pairs(spec, h_local, L)
+    flops_total = rk.sum(4.0 * D * pairs_local)
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+    sampler = ClockSampler(local_rank)   # every rank samples its own GPU
+    sampler.start()
     step_ms = []
-    secs = timed(lambda: call(*step_inputs), args.steps, barrier, per_step=step_ms)
-    secs = reduce(secs, dist.ReduceOp.MAX if world > 1 else None)
-    clocks = sampler.stop() if rank == 0 else None
+    secs_local = timed(lambda: call(*step_inputs), args.steps, barrier, per_step=step_ms)
+    secs = rk.max(secs_local)
+    clocks = sampler.stop()
+    # step time in SM clock cycles (ms x median MHz under load of the rank's own GPU, max over ranks):
+    # the 1 -> N curve with the power cap's clock differences taken out
+    ms_x_mhz = rk.max(1e3 * secs_local / args.steps * (clocks["sm_mhz"] or 0.0))
     ops.check_status(dev)
     ms_step = 1e3 * secs / args.steps
     value = flops_total / (secs / args.steps) / 1e12
@@ -494,16 +787,33 @@ def run_gpu(args, spec, rank, local_rank, world):
     out_buf = torch.empty_like(qp)
     t_attn = timed(lambda: ops.block_sparse_fwd(qp, kp, vp, lists.idx, lists.cnt, out_row_map=perm, out=out_buf),
                    n_stage, barrier, warm=1) / n_stage
-    t_attn = reduce(t_attn, dist.ReduceOp.MAX if world > 1 else None)
+    t_attn = rk.max(t_attn)
+    # the dense call of the warm-up steps (every key block, no lists): same kernel family
+    n_dense = 3
+    t_dense = rk.max(timed(lambda: ops.block_sparse_fwd(qp, kp, vp, None, None, out_row_map=perm, out=out_buf),
+                           n_dense, barrier, warm=1) / n_dense)
     pk = peaks()
     attn_tflops = 4.0 * D * pairs_local / t_attn / 1e12          # this rank's kernel
     tensor_bytes = h_local * L * D * 2
+    # how much the lists of neighbouring query blocks (in Hilbert order) have in common: |A & B| / |A | B|
+    member = lists.to_bool_mask()
+    ranked = (lists.cnt >= 0)
+    a, b = member[:, 0:-1:2], member[:, 1::2]
+    nn = min(a.shape[1], b.shape[1])
+    both_ranked = (ranked[:, 0:-1:2][:, :nn] & ranked[:, 1::2][:, :nn])
+    inter = (a[:, :nn] & b[:, :nn]).sum(-1).float()
+    union = (a[:, :nn] | b[:, :nn]).sum(-1).float()
+    jaccard = float((inter / union)[both_ranked].mean()) if bool(both_ranked.any()) else None
+    del member, a, b
     stages = {
         "permute_ms": None if perm is None else 1e3 * t_perm,
         "permute_gbs": None if perm is None else 6 * tensor_bytes / t_perm / 1e9,
         "score_select_ms": 1e3 * t_score,
         "score_select_gbs_algorithmic": (2 * tensor_bytes + lists.idx.numel() * 4) / t_score / 1e9,
         "attention_ms": 1e3 * t_attn,
+        "dense_attention_ms": 1e3 * t_dense,
+        "dense_attention_tflops": 4.0 * D * h_local * L * L / t_dense / 1e12,
+        "adjacent_list_jaccard": jaccard,
     }
 
     if hy:
@@ -516,7 +826,7 @@ def run_gpu(args, spec, rank, local_rank, world):
                                                        out=out_buf, fine=kp_lists.fine), n_stage, barrier,
                           warm=1) / n_stage
         stages["kp_score_select_refine_ms"] = 1e3 * t_kp
-        stages["kp_attention_ms"] = 1e3 * reduce(t_kp_attn, dist.ReduceOp.MAX if world > 1 else None)
+        stages["kp_attention_ms"] = 1e3 * rk.max(t_kp_attn)
         bytes8 = kp_lists.fine.view(torch.uint8)
         kept = sum(int(((bytes8 >> b) & 1).sum()) for b in range(8))
         stages["kp_tiles_kept_frac"] = kept / (64.0 * int(kp_lists.cnt.clamp(min=0).sum()))
@@ -539,7 +849,7 @@ def run_gpu(args, spec, rank, local_rank, world):
     if not hy and not seq_layout:
         # Both guidance passes of a Wan denoising step (a reuse step: lists cached): two operator calls
         # one after the other, as the reference runs them, against the one batched call.
-        from dfsattn_b200.attention_wan import dfs_attention_cfg_pair
+        from dfsattn_b200.attention_wan import dfs_attention as wan_attention, dfs_attention_cfg_pair
         wkw = dict(skip_steps=12, cache_interval=12, layer_idx=0, sparsity=spec["sparsity"], sparsity_dcrt=0.1,
                    tile_size=16, block_size=128, video_perm=vperm)
         q2, k2, v2 = (torch.cat([t, t.flip(1)]) for t in (q, k, v))
@@ -553,8 +863,8 @@ def run_gpu(args, spec, rank, local_rank, world):
         for rnd in range(2):
             t_two = min(t_two, timed(two_calls, n_stage, barrier, warm=2 - rnd) / n_stage)
             t_pair = min(t_pair, timed(pair_call, n_stage, barrier, warm=2 - rnd) / n_stage)
-        stages["cfg_two_calls_ms"] = 1e3 * reduce(t_two, dist.ReduceOp.MAX if world > 1 else None)
-        stages["cfg_pair_call_ms"] = 1e3 * reduce(t_pair, dist.ReduceOp.MAX if world > 1 else None)
+        stages["cfg_two_calls_ms"] = 1e3 * rk.max(t_two)
+        stages["cfg_pair_call_ms"] = 1e3 * rk.max(t_pair)
         del q2, k2, v2
 
     # ---- end to end through the public API with HOST buffers ----------------
@@ -585,38 +895,55 @@ def run_gpu(args, spec, rank, local_rank, world):
                                flavor="hyvideo" if hy else "wan", layer_idx=1000, **host_kw)
 
     n_e2e = max(2, min(args.steps, 5))
-    e_secs = timed(e2e_step, n_e2e, barrier, warm=2) / n_e2e
-    e_secs = reduce(e_secs, dist.ReduceOp.MAX if world > 1 else None)
+    e_secs = rk.max(timed(e2e_step, n_e2e, barrier, warm=2) / n_e2e)
     ops.check_status(dev)
     e2e = {"value": flops_total / e_secs / 1e12, "unit": UNIT, "ms_per_call": 1e3 * e_secs,
            "h2d_bytes_per_step": 3 * tensor_bytes * world, "d2h_bytes_per_step": tensor_bytes * world}
-    if world > 1:
-        dist.barrier()
+    e2e.update(copy_rates(rk, (hq, hk, hv), hout, (dq, dk, dv), torch.empty_like(dq)))
+    # what bounds the call from below: its kernels, or its bytes crossing the host link
+    e2e["floor_ms"] = max(ms_step, e2e["copy_only_ms"])
+    del hq, hk, hv, hout, dq, dk, dv
+    rk.barrier()
+
+    extras = {}
+    if not args.no_extras:
+        del q, k, v, qp, kp, vp, out_buf, out, step_inputs
+        if seq_layout:
+            del q_seq, k_seq, v_seq
+        torch.cuda.empty_cache()
+        try:
+            if world > 1 and args.layout == "head":
+                extras["layouts"] = sequence_layouts(rk, spec, vperm, flops_total)
+        except Exception as exc:  # noqa: BLE001  (the headline line must not die with an extra)
+            extras["layouts"] = {"error": f"{type(exc).__name__}: {exc}"}
+        try:
+            extras["configs"] = other_configs(rk, args)
+        except Exception as exc:  # noqa: BLE001
+            extras["configs"] = {"error": f"{type(exc).__name__}: {exc}"}
+        ops.check_status(dev)
 
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
+            cores = host_threads()
             fl, s, note = cpu_sample(spec, args.cpu_blocks)
-            cpu = {"value": fl / s / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                   "sample": note}
+            cpu = {"value": fl / s / 1e12, "unit": UNIT, "cores": cores, "kind": "port", "sample": note}
         peak = pk["bf16_tflops_sustained"]
+        config = workload_config(args, spec, world)
+        config.update({
+            "parallelism": (f"sequence-sharded x{world}: gather from and scatter to peer shards over "
+                            f"NVLink inside the permute and attention kernels" if fused_exchange
+                            else f"sequence-sharded x{world}: NCCL all-to-all in and out around "
+                            f"head-sharded compute" if seq_layout
+                            else f"head-sharded x{world}, no collective"),
+            "l2": "inputs larger than L2 (no flush needed)", "flops_per_call": flops_total})
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "ms_per_step_stats": quartiles(step_ms),
+            "ms_x_mhz": ms_x_mhz,
             "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "grid": list(spec["grid"]), "text_tokens": spec["text"],
-                       "seq_len": L, "heads": H, "heads_per_gpu": h_local, "head_dim": D,
-                       "sparsity": spec["sparsity"], "order": spec.get("order", "hilbert3d"), "block": 128,
-                       "tile": 16,
-                       "step": "refresh call: permute + score + select + attention (+fused unpermute)",
-                       "parallelism": (f"sequence-sharded x{world}: gather from and scatter to peer shards over "
-                                       f"NVLink inside the permute and attention kernels" if fused_exchange
-                                       else f"sequence-sharded x{world}: NCCL all-to-all in and out around "
-                                       f"head-sharded compute" if seq_layout
-                                       else f"head-sharded x{world}, no collective"),
-                       "l2": "inputs larger than L2 (no flush needed)",
-                       "flops_per_call": flops_total},
+            "config": config,
             "clocks": clocks,
             "e2e": e2e,
             "gpu_launches": 6 * args.steps,
@@ -630,9 +957,9 @@ def run_gpu(args, spec, rank, local_rank, world):
                          "algorithmic_flops": 4.0 * D * pairs_local},
             "cpu_baseline": cpu,
         }
+        line.update(extras)
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    rk.close()
 
 
 def main():
@@ -644,6 +971,8 @@ def main():
     ap.add_argument("--workload", default="hunyuan_720p", choices=list(WORKLOADS))
     ap.add_argument("--cpu-blocks", type=int, default=384, help="query blocks per CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the other configurations and the sequence-sharded layouts after the headline step")
     ap.add_argument("--sparsity", type=float, default=None, help="override the workload's sparsity")
     ap.add_argument("--order", default="hilbert3d", choices=["hilbert3d", "org"],
                     help="token order: 3-D Hilbert curve or raster (no permutation)")

@@ -52,11 +52,7 @@ SIGNATURES = {
     "dfs_qkv_prepare": (c_int, [c_void_p] * 5 + [c_float, c_float, c_int, c_void_p, c_void_p, c_int, c_int64,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int,
                                 c_void_p]),
-}
-
-# testing hooks exported by the library but not part of the public header
-_DEBUG_SIGNATURES = {
-    "dfs_debug_set_dump": (None, [c_void_p]),
+    "dfs_selftest_wait_timeout": (c_int, [c_int64, c_void_p, c_void_p]),
 }
 
 
@@ -70,14 +66,13 @@ def _load():
             f"{LIB_PATH} is missing: build it with `python dfsattn_b200/build.py` "
             "(there is no CPU or PyTorch fallback)")
     lib = ctypes.CDLL(LIB_PATH)
-    for table in (SIGNATURES, _DEBUG_SIGNATURES):
-        for name, (res, args) in table.items():
-            try:
-                fn = getattr(lib, name)
-            except AttributeError as exc:
-                raise DfsLibraryError(f"{LIB_PATH} does not export {name}") from exc
-            fn.restype = res
-            fn.argtypes = args
+    for name, (res, args) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as exc:
+            raise DfsLibraryError(f"{LIB_PATH} does not export {name}") from exc
+        fn.restype = res
+        fn.argtypes = args
     return lib
 
 

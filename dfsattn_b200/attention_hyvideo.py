@@ -123,6 +123,8 @@ class DFS_Attention(nn.Module):
                             self.block_size, self.q_tile_size, self.fine_top_p, kp_allowed=self.flavor == "hyvideo")
         out_dtype = q.dtype
         device = q.device
+        ops._need_cuda(q, k, v)
+        ops.poll_status(device)   # raises if a kernel of an earlier call gave up on a wait
         seq_len = q.shape[2]
         video_len = self._video_len(seq_len)
         rec = DFS_Attention.timing_recorder

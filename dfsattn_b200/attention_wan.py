@@ -60,6 +60,8 @@ class DFS_Attention(_hy.DFS_Attention):
         _hy._reject_unsupported(self.sparse_execution, self.selector_mode, self.block_top_p, self.token_top_k,
                                 self.block_size, self.q_tile_size)
         out_dtype, device = q.dtype, q.device
+        ops._need_cuda(q, k, v)
+        ops.poll_status(device)   # raises if a kernel of an earlier call gave up on a wait
         _, H, L, D = q.shape
         if engine.valid_length(cu_seqlens_q, L) != L:
             raise ValueError("a padded tail is not supported for a batched pair")

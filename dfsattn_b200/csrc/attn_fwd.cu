@@ -82,7 +82,6 @@ struct Params {
   const int32_t* out_row_map;
   __nv_bfloat16* out;
   int32_t* status;
-  float* debug;         // optional dump for (query block 0, head 0): S of the first tile, O, l, m
   long long seq_len;
   long long kv_len;
   long long out_head_stride;   // elements between heads of the output
@@ -450,7 +449,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     float m_a = -INFINITY, m_b = -INFINITY;  // reference maxima (raw score units) of the two rows
     uint64_t la0 = pack2(0.f, 0.f), la1 = la0, lb0 = la0, lb1 = la0;  // partial row sums (this thread's columns)
     bool ok = true;
-    const bool dump = p.debug != nullptr && qb == 0 && head == 0 && n_tiles > 0;
     const uint32_t o_addr = tmem_base + lane_sel + kColO;
     int kb_next = n_tiles > 0 ? (my_idx ? __ldg(my_idx) : 0) : 0;
     // tile map byte of this warp's query tile for the current and the next listed block
@@ -492,16 +490,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       tmem_ld_16x256b_x16(s_addr, r);
       tmem_wait_ld();
       if (valid < kBlockN) mask_tail(r, valid, t4);
-      if (dump && j == 0) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int col = 8 * i + 2 * t4;
-          p.debug[row_a * 128 + col] = __uint_as_float(r[4 * i]);
-          p.debug[row_a * 128 + col + 1] = __uint_as_float(r[4 * i + 1]);
-          p.debug[row_b * 128 + col] = __uint_as_float(r[4 * i + 2]);
-          p.debug[row_b * 128 + col + 1] = __uint_as_float(r[4 * i + 3]);
-        }
-      }
 
       // The reference maximum of a row moves only when a tile exceeds it by more than the
       // threshold, which is rare after the first tile.  So the exponentials are taken against the
@@ -513,10 +501,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       float mt_a = -INFINITY, mt_b = -INFINITY;
       bool redo = true;  // the exp2 pass against the final reference is still to be done
       if (kSpeculate && j > 0) {
-        // finite without tile maps: every row saw a key in the first tile; with them a row may still
-        // be without a reference (-inf), which the redo below then settles
-        const float nma = (kFine && m_a == -INFINITY) ? 0.f : -m_a * c;
-        const float nmb = (kFine && m_b == -INFINITY) ? 0.f : -m_b * c;
+        // a row may still be without a reference (-inf): every key it has seen so far was dropped by a
+        // tile map or lies past kv_len; the redo below then settles it
+        const float nma = (m_a == -INFINITY) ? 0.f : -m_a * c;
+        const float nmb = (m_b == -INFINITY) ? 0.f : -m_b * c;
         exp_pass<kPolyGroups, true, kFine>(r, c2, pack2(nma, nma), pack2(nmb, nmb), packed, ta0, ta1, tb0, tb1, mt_a,
                                            mt_b, keep);
       } else {
@@ -652,12 +640,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int col = h * 64 + 8 * i + 2 * t4;
-          if (dump) {
-            p.debug[128 * 128 + row_a * HD + col] = __uint_as_float(o[4 * i]);
-            p.debug[128 * 128 + row_a * HD + col + 1] = __uint_as_float(o[4 * i + 1]);
-            p.debug[128 * 128 + row_b * HD + col] = __uint_as_float(o[4 * i + 2]);
-            p.debug[128 * 128 + row_b * HD + col + 1] = __uint_as_float(o[4 * i + 3]);
-          }
           if (live_a)
             *reinterpret_cast<uint32_t*>(out_a + col) =
                 cvt_bf16x2(__uint_as_float(o[4 * i]) * inv_a, __uint_as_float(o[4 * i + 1]) * inv_a);
@@ -665,12 +647,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             *reinterpret_cast<uint32_t*>(out_b + col) =
                 cvt_bf16x2(__uint_as_float(o[4 * i + 2]) * inv_b, __uint_as_float(o[4 * i + 3]) * inv_b);
         }
-      }
-      if (dump && t4 == 0) {
-        p.debug[128 * 128 + 128 * HD + row_a] = l_a;
-        p.debug[128 * 128 + 128 * HD + row_b] = l_b;
-        p.debug[128 * 128 + 128 * HD + 128 + row_a] = m_a;
-        p.debug[128 * 128 + 128 * HD + 128 + row_b] = m_b;
       }
     }
   }
@@ -707,11 +683,6 @@ int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& 
 }
 
 }  // namespace
-
-// Testing hook (not part of the public header): optional dump buffer for the CTA of
-// (query block 0, head 0): raw scores of its first tile, un-normalised O, row sums, row maxima.
-static float* g_debug_buffer = nullptr;
-extern "C" void dfs_debug_set_dump(float* device_buffer) { g_debug_buffer = device_buffer; }
 
 namespace {
 struct ShardedOut {
@@ -764,7 +735,6 @@ int block_sparse_fwd_impl(const void* q, const void* k, const void* v, const int
   p.out_row_map = out_row_map;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.status = status;
-  p.debug = g_debug_buffer;
   p.seq_len = seq_len;
   p.kv_len = kv_len;
   // per batch element [H, L, D] or, token-major, [L, H*D]
@@ -788,6 +758,31 @@ int block_sparse_fwd_impl(const void* q, const void* k, const void* v, const int
                          : launch_fwd<64, false>(mq, mk, mv, p, all_heads, stream);
 }
 }  // namespace
+
+namespace {
+// One warp waits on a barrier that nothing completes and leaves as the attention kernel does after
+// an expired wait: flag in shared memory, CTA-wide barrier, one thread reports to the status word.
+__global__ void wait_timeout_selftest_kernel(int32_t* status, long long limit_cycles) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag[2];
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag[0] = abort_flag[1] = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait_bounded(&bar, 0, abort_flag, limit_cycles);
+  __syncthreads();
+  if (abort_flag[0] != 0 && threadIdx.x == 0 && status) atomicExch(status, DFS_STATUS_WAIT_TIMEOUT);
+}
+}  // namespace
+
+extern "C" int dfs_selftest_wait_timeout(int64_t limit_cycles, int32_t* status, void* stream) {
+  if (status == nullptr) return DFS_ERR_NULL;
+  if (limit_cycles < 1 || limit_cycles >= (1LL << 31)) return DFS_ERR_RANGE;
+  wait_timeout_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(status, limit_cycles);
+  return static_cast<int>(cudaGetLastError());
+}
 
 extern "C" int dfs_block_sparse_fwd_ex(const void* q, const void* k, const void* v, const int32_t* idx,
                                        const int32_t* cnt, int kmax, const int32_t* out_row_map, void* out,

@@ -96,13 +96,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr long long kWaitLimitCycles = 400000000LL;  // about 0.2 s
 
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
-                                                  volatile int* abort_flag) {
+                                                  volatile int* abort_flag,
+                                                  long long limit_cycles = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag != 0) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > limit_cycles) {
       *abort_flag = 1;
       return false;
     }

@@ -1,9 +1,12 @@
 // Row gather along the token axis: dst[h, i, :] = src[h, perm[i], :].
 //
-// HBM-bound byte copy.  One thread moves one 16-byte chunk; consecutive
-// threads cover one row's chunks, so every row is read and written as whole
-// 128/256/512-byte segments.  Algorithmic traffic = 2 * bytes(tensor) plus the
-// 4-byte index per row.
+// HBM-bound byte copy.  One thread moves 16-byte chunks; consecutive threads cover one row's
+// chunks, so every row is read and written as whole 128/256/512-byte segments.  A thread handles
+// four chunks (a grid stride apart) per trip: the four index loads go out together, then the four
+// row loads, then the four stores, so that a warp keeps 2 KB of reads in flight instead of 512
+// bytes.  Index arithmetic is 32-bit (a head has fewer than 2^31 chunks; checked by the launcher),
+// with a shift when a row is a power-of-two number of chunks.  Algorithmic traffic =
+// 2 * bytes(tensor) plus the 4-byte index per row.
 #include "common.cuh"
 
 namespace {
@@ -13,21 +16,57 @@ struct PermuteArgs {
   uint4* dst[3];
 };
 
+constexpr int kPermuteBatch = 4;
+
+// chunk index within a head -> (row, column) with chunks_per_row = 1 << shift, or a division
+template <bool kPow2>
+__device__ __forceinline__ void split_chunk(unsigned c, unsigned chunks_per_row, int shift, unsigned& row,
+                                            unsigned& col) {
+  if (kPow2) {
+    row = c >> shift;
+    col = c & (chunks_per_row - 1u);
+  } else {
+    row = c / chunks_per_row;
+    col = c - row * chunks_per_row;
+  }
+}
+
+template <bool kPow2>
 __global__ void __launch_bounds__(256) permute_rows_kernel(PermuteArgs args, const int32_t* __restrict__ perm,
-                                                           long long seq_len, int chunks_per_row,
-                                                           long long chunks_per_head) {
+                                                           unsigned chunks_per_row, int shift,
+                                                           unsigned chunks_per_head) {
   const int which = blockIdx.z;
   const int head = blockIdx.y;
   // selects instead of a dynamic index keep the argument struct out of local memory
   const uint4* __restrict__ src = which == 0 ? args.src[0] : (which == 1 ? args.src[1] : args.src[2]);
   uint4* __restrict__ dst = which == 0 ? args.dst[0] : (which == 1 ? args.dst[1] : args.dst[2]);
-  const long long base = static_cast<long long>(head) * chunks_per_head;
-  for (long long c = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; c < chunks_per_head;
-       c += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long row = c / chunks_per_row;
-    const int col = static_cast<int>(c - row * chunks_per_row);
-    const long long from = static_cast<long long>(__ldg(perm + row));
-    dst[base + c] = __ldg(src + base + from * chunks_per_row + col);
+  const size_t base = static_cast<size_t>(head) * chunks_per_head;
+  src += base;
+  dst += base;
+  const unsigned stride = gridDim.x * blockDim.x;
+  unsigned c = blockIdx.x * blockDim.x + threadIdx.x;
+  // chunks_per_head < 2^31 and stride < 2^21, so c + 3 * stride cannot wrap
+  for (; c + (kPermuteBatch - 1) * stride < chunks_per_head; c += kPermuteBatch * stride) {
+    unsigned col[kPermuteBatch];
+    int from[kPermuteBatch];
+    uint4 val[kPermuteBatch];
+#pragma unroll
+    for (int b = 0; b < kPermuteBatch; ++b) {
+      unsigned row;
+      split_chunk<kPow2>(c + b * stride, chunks_per_row, shift, row, col[b]);
+      from[b] = __ldg(perm + row);
+    }
+#pragma unroll
+    for (int b = 0; b < kPermuteBatch; ++b)
+      val[b] = __ldcs(src + static_cast<size_t>(from[b]) * chunks_per_row + col[b]);
+#pragma unroll
+    for (int b = 0; b < kPermuteBatch; ++b) __stcs(dst + c + b * stride, val[b]);
+  }
+  for (; c < chunks_per_head; c += stride) {
+    unsigned row, col;
+    split_chunk<kPow2>(c, chunks_per_row, shift, row, col);
+    const int from = __ldg(perm + row);
+    __stcs(dst + c, __ldcs(src + static_cast<size_t>(from) * chunks_per_row + col));
   }
 }
 
@@ -49,12 +88,20 @@ int launch_permute(const void* const* srcs, void* const* dsts, int n, const int3
   if (m == 0) return 0;
   const int chunks_per_row = row_bytes / 16;
   const long long chunks_per_head = static_cast<long long>(seq_len) * chunks_per_row;
-  long long blocks = (chunks_per_head + 255) / 256;
+  if (chunks_per_head >= (1LL << 31)) return DFS_ERR_SHAPE;
+  long long blocks = (chunks_per_head + 256 * kPermuteBatch - 1) / (256 * kPermuteBatch);
   // a few waves of 148 SMs x 8 resident CTAs; the grid-stride loop covers the rest
   const long long cap = 148LL * 8 * 4;
   if (blocks > cap) blocks = cap;
   dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(heads), static_cast<unsigned>(m));
-  permute_rows_kernel<<<grid, 256, 0, stream>>>(args, perm, seq_len, chunks_per_row, chunks_per_head);
+  int shift = 0;
+  while ((1 << shift) < chunks_per_row) ++shift;
+  if ((1 << shift) == chunks_per_row)
+    permute_rows_kernel<true><<<grid, 256, 0, stream>>>(args, perm, chunks_per_row, shift,
+                                                        static_cast<unsigned>(chunks_per_head));
+  else
+    permute_rows_kernel<false><<<grid, 256, 0, stream>>>(args, perm, chunks_per_row, 0,
+                                                         static_cast<unsigned>(chunks_per_head));
   return static_cast<int>(cudaGetLastError());
 }
 

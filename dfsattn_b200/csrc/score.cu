@@ -21,6 +21,8 @@
 // (different summation order, 2^-16 operand split).
 #include <math.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace {
@@ -722,20 +724,26 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 namespace {
 // Device address of g_static_scratch per device.  In host code the symbol's
 // name is only a handle; the address a kernel can use comes from
-// cudaGetSymbolAddress, asked once per device with that device current.
-char* g_static_scratch_addr[kMaxDevices] = {};
+// cudaGetSymbolAddress, asked once per device with that device current.  The
+// slots are atomics: two host threads that make the first call on one device at
+// the same time both look the address up and store the same value.  The address
+// belongs to the device's primary context: after cudaDeviceReset() the slot is
+// stale (the process must not call this entry point again on that device).
+std::atomic<char*> g_static_scratch_addr[kMaxDevices];
 
 int static_scratch_for_current_device(char** out) {
   int dev = -1;
   DFS_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return DFS_ERR_RANGE;
-  if (g_static_scratch_addr[dev] == nullptr) {
+  char* addr = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+  if (addr == nullptr) {
     void* ptr = nullptr;
     DFS_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_static_scratch));
     if (ptr == nullptr) return DFS_ERR_NULL;
-    g_static_scratch_addr[dev] = static_cast<char*>(ptr);
+    addr = static_cast<char*>(ptr);
+    g_static_scratch_addr[dev].store(addr, std::memory_order_release);
   }
-  *out = g_static_scratch_addr[dev];
+  *out = addr;
   return 0;
 }
 }  // namespace

@@ -92,20 +92,32 @@ class BlockLists:
 
 
 class PermutationCache:
-    """int32 (perm, inverse) on the device, keyed by the permutation's identity."""
+    """int32 (perm, inverse) on the device per (permutation, lengths, device).
 
-    def __init__(self):
-        self._cache: Dict[tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+    An entry is found by the identity of the ``video_perm`` tensor (and its version counter); the
+    entry holds a reference to that tensor, so its address cannot be handed to another permutation
+    while the entry lives.  A tensor that is not known by identity is compared by CONTENT with the
+    cached ones of the same length before anything is rebuilt (a caller that builds an equal
+    permutation anew for every call still hits).  At most ``max_entries`` entries are kept."""
+
+    def __init__(self, max_entries: int = 16):
+        self._cache: Dict[tuple, tuple] = {}
+        self.max_entries = max_entries
 
     def get(self, video_perm: Optional[torch.Tensor], seq_len: int, video_len: int,
             device: torch.device) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
         if video_perm is None:
             return None, None  # raster order: no gather at all
-        key = (video_perm.data_ptr(), int(video_perm.numel()), int(video_perm._version), seq_len,
-               video_len, str(device))
+        shape_key = (int(video_perm.numel()), seq_len, video_len, str(device))
+        key = (id(video_perm), int(video_perm._version)) + shape_key
         hit = self._cache.get(key)
-        if hit is not None:
-            return hit
+        if hit is not None and hit[0] is video_perm:
+            return hit[1], hit[2]
+        for other_key, (src, perm, inv) in list(self._cache.items()):
+            if other_key[2:] == shape_key and src.device == video_perm.device and src.dtype == video_perm.dtype \
+                    and src._version == other_key[1] and torch.equal(src, video_perm):
+                self._store(key, (video_perm, perm, inv))
+                return perm, inv
         if video_perm.numel() != video_len:
             raise ValueError(f"video_perm has {video_perm.numel()} entries, expected video_len={video_len}")
         if seq_len >= 2 ** 31:
@@ -118,8 +130,13 @@ class PermutationCache:
         inv = torch.empty_like(perm)
         inv[perm] = torch.arange(seq_len, device=device, dtype=torch.int64)
         out = (perm.to(torch.int32).contiguous(), inv.to(torch.int32).contiguous())
-        self._cache[key] = out
+        self._store(key, (video_perm,) + out)
         return out
+
+    def _store(self, key, entry):
+        while len(self._cache) >= self.max_entries:
+            self._cache.pop(next(iter(self._cache)))
+        self._cache[key] = entry
 
     def clear(self):
         self._cache.clear()

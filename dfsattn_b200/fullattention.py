@@ -5,7 +5,7 @@ the processors use (``"flash"``: varlen attention with cu_seqlens = [0, valid,
 L]).  It is the block-sparse kernel with every key block listed -- one
 back-end, no flash-attn dependency.
 """
-from . import engine
+from . import engine, ops
 
 
 def full_attention(q, k, v, mode="flash", drop_rate=0, attn_mask=None, causal=False, cu_seqlens_q=None,
@@ -23,6 +23,8 @@ def full_attention(q, k, v, mode="flash", drop_rate=0, attn_mask=None, causal=Fa
         raise ValueError("dense attention here is non-causal and without dropout")
     out_dtype = q.dtype
     L = q.shape[2]
+    ops._need_cuda(q, k, v)
+    ops.poll_status(q.device)   # raises if a kernel of an earlier call gave up on a wait
     qh, kh, vh = engine.prepare_inputs(q, k, v)
     valid = engine.valid_length(cu_seqlens_kv if cu_seqlens_kv is not None else cu_seqlens_q, L)
     out = engine.run_attention(qh, kh, vh, None, out_row_map, valid, token_major=token_major_out,

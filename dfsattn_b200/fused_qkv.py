@@ -47,6 +47,22 @@ def norm_params(module, heads: int, width: int):
     return weight.detach().to(torch.bfloat16).contiguous(), float(eps), across
 
 
+def _cached_tables(sources, device, build):
+    """Tables converted from `sources` (a tuple of tensors), cached per source tensors: an entry
+    keeps references to its sources (their addresses cannot be reused while it lives) and is valid
+    only for the very same, unmodified tensor objects."""
+    key = tuple(id(t) for t in sources) + (str(device),)
+    versions = tuple(int(t._version) for t in sources)
+    hit = _table_cache.get(key)
+    if hit is not None and all(a is b for a, b in zip(hit[0], sources)) and hit[1] == versions:
+        return hit[2]
+    tables = build()
+    if len(_table_cache) >= 8:
+        _table_cache.clear()
+    _table_cache[key] = (tuple(sources), versions, tables)
+    return tables
+
+
 def rope_tables(rotary, device) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
     """fp32 2-D (cos, sin) tables from (cos, sin) [S, D] (HunyuanVideo) or complex frequencies
     [1, 1, S, D/2] / a (real, imag) pair (Wan).  Conversions are cached per source tensor."""
@@ -55,26 +71,15 @@ def rope_tables(rotary, device) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
     if isinstance(rotary, torch.Tensor):
         if not rotary.is_complex():
             raise TypeError("a single rotary tensor must be complex")
-        key = (rotary.data_ptr(), tuple(rotary.shape), str(device))
-        hit = _table_cache.get(key)
-        if hit is None:
+
+        def split():
             flat = rotary.reshape(-1, rotary.shape[-1])
-            hit = (flat.real.to(device=device, dtype=torch.float32).contiguous(),
-                   flat.imag.to(device=device, dtype=torch.float32).contiguous())
-            if len(_table_cache) >= 8:
-                _table_cache.clear()
-            _table_cache[key] = hit
-        return hit
+            return (flat.real.to(device=device, dtype=torch.float32).contiguous(),
+                    flat.imag.to(device=device, dtype=torch.float32).contiguous())
+        return _cached_tables((rotary,), device, split)
     cos, sin = rotary
-    key = (cos.data_ptr(), sin.data_ptr(), tuple(cos.shape), str(device))
-    hit = _table_cache.get(key)
-    if hit is None:
-        hit = tuple(t.reshape(-1, t.shape[-1]).to(device=device, dtype=torch.float32).contiguous()
-                    for t in (cos, sin))
-        if len(_table_cache) >= 8:
-            _table_cache.clear()
-        _table_cache[key] = hit
-    return hit
+    return _cached_tables((cos, sin), device, lambda: tuple(
+        t.reshape(-1, t.shape[-1]).to(device=device, dtype=torch.float32).contiguous() for t in (cos, sin)))
 
 
 def token_perm(video_perm, seq_len: int, video_len: int, device):

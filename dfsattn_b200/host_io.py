@@ -4,11 +4,16 @@
 buffers: heads are independent on the whole path, so the heads are cut into
 groups and the host->device copy of group g+1, the attention of group g and the
 device->host copy of group g-1 run concurrently on three CUDA streams (uploads are
-queued two groups ahead, into one device staging buffer allocated per call).  Each
+queued two groups ahead).  The two copy streams and the device staging buffer are
+created once per (device, shape) and reused by later calls.  Each
 group keeps its own mask-cache entry (cache key ``(layer_idx, group)``), so the
 refresh / reuse schedule of the operator is unchanged.  The first three and the
 last two groups are single heads when there are enough heads: the first upload and
 the last download are the only copies nothing overlaps, so they are kept short.
+
+By default the call returns once the last download has landed (it waits on one
+event), so ``out`` can be read and q, k, v reused straight away.  With
+``wait=False`` it returns at once and hands back the event to wait on.
 """
 from typing import Optional
 
@@ -35,12 +40,35 @@ def group_bounds(heads: int, groups: int, ramp: bool = True):
     return bounds
 
 
+_resources = {}
+
+
+def _stream_set(dev: torch.device, shape, dtype):
+    """Copy streams and the staging buffer [3, H, L, D] of a (device, shape): made on first use."""
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), tuple(shape), dtype)
+    res = _resources.get(key)
+    if res is None:
+        if len(_resources) >= 4:   # a caller cycling through shapes keeps the four latest
+            _resources.pop(next(iter(_resources)))
+        res = {"copy_in": torch.cuda.Stream(dev), "copy_out": torch.cuda.Stream(dev),
+               "stage": torch.empty((3,) + tuple(shape), dtype=dtype, device=dev)}
+        _resources[key] = res
+    return res
+
+
+def release_resources():
+    """Drop the cached copy streams and staging buffers."""
+    _resources.clear()
+
+
 def dfs_attention_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: Optional[torch.Tensor] = None,
                        head_groups: int = 12, device="cuda", flavor: str = "hyvideo", layer_idx: int = 0,
-                       ramp: bool = True, **kwargs) -> torch.Tensor:
+                       ramp: bool = True, wait: bool = True, **kwargs):
     """q, k, v: host tensors [1, H, L, D] (pinned memory makes the copies asynchronous).
-    Returns the host tensor ``out`` ([1, H, L, D], pinned if allocated here).  ``kwargs`` are those of
-    ``dfs_attention`` (step_idx, skip_steps, cache_interval, sparsity, ..., video_perm)."""
+    Returns the host tensor ``out`` ([1, H, L, D], pinned if allocated here); with ``wait=False``
+    returns ``(out, event)`` without waiting: ``out`` must not be read, nor q, k, v overwritten,
+    before ``event.synchronize()``.  ``kwargs`` are those of ``dfs_attention`` (step_idx, skip_steps,
+    cache_interval, sparsity, ..., video_perm)."""
     if q.is_cuda or k.is_cuda or v.is_cuda:
         raise ValueError("dfs_attention_host takes host tensors; use dfs_attention for device tensors")
     fn = attention_hyvideo.dfs_attention if flavor == "hyvideo" else attention_wan.dfs_attention
@@ -51,10 +79,9 @@ def dfs_attention_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: O
     if out is None:
         out = torch.empty(q.shape, dtype=q.dtype).pin_memory()
     compute = torch.cuda.current_stream(dev)
-    copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    # one device staging buffer for all three tensors: a single allocation per call
-    stage = torch.empty((3,) + tuple(q.shape[1:]), dtype=q.dtype, device=dev)
-    stage.record_stream(copy_in)
+    res = _stream_set(dev, q.shape[1:], q.dtype)
+    copy_in, copy_out, stage = res["copy_in"], res["copy_out"], res["stage"]
+    # the staging buffer is reused: this call's uploads follow whatever the stream did before
     copy_in.wait_stream(compute)
     uploaded = []
 
@@ -83,6 +110,11 @@ def dfs_attention_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: O
             copy_out.wait_event(done)
             o.record_stream(copy_out)
             out[:, h0:h1].copy_(o, non_blocking=True)
+    landed = torch.cuda.Event()
+    landed.record(copy_out)
     compute.wait_stream(copy_out)
     compute.wait_stream(copy_in)
+    if not wait:
+        return out, landed
+    landed.synchronize()
     return out

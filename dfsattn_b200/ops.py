@@ -31,16 +31,33 @@ def _need_cuda(*tensors):
 
 
 # ---- status word ------------------------------------------------------------
+# One int32 per device that a kernel sets when one of its bounded waits ran out.  The word is
+# sticky: once it is set, CTAs that start later return at once, so an operator must not go on
+# handing out results.  Every operator call therefore polls it (below) without stalling the stream.
 _status = {}
+_monitors = {}
+
+
+def _device_key(device) -> int:
+    device = torch.device(device)
+    return device.index if device.index is not None else torch.cuda.current_device()
 
 
 def status_tensor(device) -> torch.Tensor:
     """Per-device int32 word that kernels set when a bounded wait expired."""
-    device = torch.device(device)
-    key = device.index if device.index is not None else torch.cuda.current_device()
+    key = _device_key(device)
     if key not in _status:
-        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
     return _status[key]
+
+
+_STATUS_NAMES = {1: "a bounded wait inside a kernel expired", 2: "dynamic shared memory was not 1 KB aligned"}
+
+
+def _raise_status(word: torch.Tensor, code: int):
+    word.zero_()
+    raise RuntimeError(f"dfsattn_b200 kernel reported device status {code} "
+                       f"({_STATUS_NAMES.get(code, 'unknown code')}); results since the last check are invalid")
 
 
 def check_status(device=None):
@@ -48,9 +65,37 @@ def check_status(device=None):
     device = torch.device("cuda" if device is None else device)
     word = status_tensor(device)
     code = int(word.item())
+    mon = _monitors.get(_device_key(device))
+    if mon is not None:
+        mon["event"] = None
     if code != 0:
-        word.zero_()
-        raise RuntimeError(f"dfsattn_b200 kernel reported device status {code} (bounded wait expired)")
+        _raise_status(word, code)
+
+
+def poll_status(device):
+    """Called at the start of every operator call: look at the copy of the status word that the
+    PREVIOUS call queued (if that copy has finished; no wait otherwise), raise ``RuntimeError`` and
+    clear the word if it was set, then queue a fresh asynchronous copy into pinned host memory
+    behind the work already on the current stream.  A give-up is therefore reported one call late
+    at the latest once the stream has drained, and without any synchronisation on the fast path."""
+    key = _device_key(device)
+    word = status_tensor(device)
+    mon = _monitors.get(key)
+    if mon is None:
+        mon = {"host": torch.zeros(1, dtype=torch.int32).pin_memory(), "event": None}
+        _monitors[key] = mon
+    ev = mon["event"]
+    if ev is not None and ev.query():
+        mon["event"] = None
+        code = int(mon["host"][0])
+        if code != 0:
+            mon["host"][0] = 0
+            _raise_status(word, code)
+    if mon["event"] is None:
+        mon["host"].copy_(word, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(torch.device("cuda", key)))
+        mon["event"] = ev
 
 
 # ---- host helpers -------------------------------------------------------------

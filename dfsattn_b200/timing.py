@@ -1,8 +1,9 @@
 """CUDA-event phase timing resolved lazily (mirrors dfsattn/utils/timing.py:24-218).
 
 Events are recorded around a region without synchronising; durations are
-computed only when ``dump_csv`` / ``summary`` is called.  Phases used by the
-native path: ``topk_mask``, ``topk_routing``, ``attention_execution``.
+computed only when ``dump_csv`` / ``summary`` is called.  Phases recorded by the
+native path: ``topk_mask``, ``topk_routing``, ``attention_execution``; the written
+table has the reference's columns and categories.
 """
 import csv
 import os
@@ -67,16 +68,32 @@ class AttentionTimingRecorder:
             agg["mean_ms"] = agg["total_ms"] / max(agg["calls"], 1)
         return out
 
+    # raw phase name -> category of the written table (dfsattn/utils/timing.py:148-151): the selector's
+    # ``topk_mask`` events are reported as ``top_k_selection``; ``topk_routing`` encloses ``topk_mask`` and
+    # is not written, as in the reference
+    CATEGORIES = {"topk_mask": "top_k_selection", "attention_execution": "attention_execution"}
+
     def dump_csv(self, output_path: str, extra_totals: Optional[Dict[str, float]] = None):
-        summary = self.summary()
+        """One aggregate row per category, columns ``phase,total_ms,calls,mean_ms`` as the reference
+        writes them (dfsattn/utils/timing.py:140-200); ``extra_totals`` become rows of one call each.
+        Returns the same table as a dict (the raw per-phase table stays available from ``summary``)."""
+        totals = {name: 0.0 for name in self.CATEGORIES.values()}
+        calls = {name: 0 for name in totals}
+        for phase, _, _, ms in self._resolve():
+            cat = self.CATEGORIES.get(phase)
+            if cat is not None:
+                totals[cat] += ms
+                calls[cat] += 1
+        for name, value in (extra_totals or {}).items():
+            totals[name] = float(value)
+            calls[name] = 1
         os.makedirs(os.path.dirname(output_path) or ".", exist_ok=True)
         with open(output_path, "w", newline="") as f:
-            w = csv.writer(f)
-            w.writerow(["phase", "calls", "total_ms", "mean_ms"])
-            for phase, agg in sorted(summary.items()):
-                w.writerow([phase, agg["calls"], f"{agg['total_ms']:.6f}", f"{agg['mean_ms']:.6f}"])
-            for name, value in (extra_totals or {}).items():
-                w.writerow([name, 1, f"{float(value):.6f}", f"{float(value):.6f}"])
-            for name, values in sorted(self._metric_records.items()):
-                w.writerow([name, len(values), f"{sum(values):.6f}", f"{sum(values) / len(values):.6f}"])
-        return summary
+            w = csv.DictWriter(f, fieldnames=["phase", "total_ms", "calls", "mean_ms"])
+            w.writeheader()
+            for name, total in totals.items():
+                w.writerow({"phase": name, "total_ms": total, "calls": calls[name],
+                            "mean_ms": total / calls[name] if calls[name] else 0.0})
+        return {name: {"calls": float(calls[name]), "total_ms": total,
+                       "mean_ms": total / calls[name] if calls[name] else 0.0}
+                for name, total in totals.items()}

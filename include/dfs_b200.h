@@ -20,7 +20,10 @@
  *    the fixed scratch array of dfs_block_scores_static); nothing else.
  *  - Kernels never trap: every wait inside a kernel is bounded; a kernel that
  *    gives up writes a non-zero code to `*status` (device int32, caller
- *    zero-initialised, may be NULL for kernels that have no waits).
+ *    zero-initialised, may be NULL for kernels that have no waits).  The word
+ *    is sticky: while it is non-zero, CTAs that start later return at once, so
+ *    the caller must read it back (asynchronously is enough), discard the
+ *    results produced since its last look and zero it before going on.
  */
 #ifndef DFS_B200_H
 #define DFS_B200_H
@@ -190,6 +193,9 @@ int dfs_block_scores(const void* q_perm, const void* k_perm, int dtype, int head
  *    are rejected with DFS_ERR_STATIC_SCRATCH; nothing is launched.
  *  - The first call on each device looks up the array's device address (with
  *    that device current); make that first call outside any stream capture.
+ *    The address is kept per device ordinal for the life of the process:
+ *    after cudaDeviceReset() on a device this entry point must not be used on
+ *    it again.  Concurrent first calls from several host threads are safe.
  *  - The call allocates nothing and frees nothing.
  *  - All calls on a device share the one array, which keeps the previous
  *    call's contents; nothing in it needs to be cleared between calls (every
@@ -295,6 +301,16 @@ int dfs_block_sparse_fwd_batched(const void* q, const void* k, const void* v, co
                                  int out_token_major, int batch, int heads, int64_t seq_len,
                                  int64_t kv_len, int head_dim, float scale, int32_t* status,
                                  void* stream);
+
+/* ---- diagnostics ----------------------------------------------------------- */
+
+/* Exercises the give-up path of the kernels' bounded waits without any other work: one small
+ * CTA waits, for at most limit_cycles SM clock cycles, on a barrier that nothing ever completes,
+ * then leaves through the same tear-down as the attention kernel and writes
+ * DFS_STATUS_WAIT_TIMEOUT to *status.  No counterpart in the reference (which has no bounded
+ * waits); it lets a host verify its handling of the status word on a healthy GPU.
+ * limit_cycles must be in [1, 2^31). */
+int dfs_selftest_wait_timeout(int64_t limit_cycles, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -13,6 +13,8 @@ stops at the first failure has already run every other test.
 import pytest
 import torch
 
+import oracle
+
 pytestmark = pytest.mark.gpu
 
 
@@ -54,6 +56,13 @@ def test_static_scratch_scores_equal_workspace_scores_twice_in_a_row(ops):
         # same kernels, same inputs: the tolerance of the scoring tests (rtol 2e-4) and in fact bit-equal
         torch.testing.assert_close(got, want, rtol=2e-4, atol=1e-6)
         assert torch.equal(got, want)
+        # and against the CPU oracle of the reference's scoring on the same values (inputs are already in
+        # the permuted order: identity permutation)
+        qc, kc = q.float().cpu()[None], k.float().cpu()[None]
+        ident = torch.arange(L)
+        ref = (oracle.block_scores_wan(qc, kc, ident) if wan
+               else oracle.block_scores_hyvideo(qc, kc, ident, video_len))[0]
+        torch.testing.assert_close(got.cpu(), ref, rtol=2e-4, atol=1e-6)
 
 
 def test_static_scratch_rejects_shapes_beyond_its_size(ops):
