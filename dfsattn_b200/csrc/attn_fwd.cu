@@ -41,6 +41,8 @@
 //
 // Every wait is bounded; on expiry the CTA records DFS_STATUS_WAIT_TIMEOUT,
 // drains its copies and MMAs in flight, frees its TMEM and returns.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace {
@@ -50,7 +52,8 @@ using namespace dfs;
 constexpr int kBlockM = 128;  // query rows per CTA
 constexpr int kBlockN = 128;  // keys per tile
 constexpr int kThreads = 384;
-constexpr int kStages = 3;
+constexpr int kStagesSingle = 3;  // K and V ring depth, one CTA per query block
+constexpr int kStagesPair = 3;    // the same for a CTA of a pair (its stages are half as large)
 constexpr uint32_t kTmemCols = 512;
 // Tensor memory: three score buffers of 128 fp32 columns and the output accumulator.  P(j) (packed
 // bf16 pairs, 64 columns) is written over the first half of the score buffer it was computed from:
@@ -60,16 +63,22 @@ constexpr uint32_t kColO = 384;
 __device__ __forceinline__ uint32_t s_col(int j) { return static_cast<uint32_t>(j % kSBufs) * 128u; }
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
-template <int HD>
+// kPair: the CTA is one of a pair that shares every K and V tile (see the pair notes at the kernel).
+// It then holds HALF of each: 64 of the 128 keys of a K tile (all dims: boxes of [64 rows][64 bf16]) and 64
+// of the 128 dims of a V tile (all keys: one [128 rows][64 bf16] box).
+template <int HD, bool kPair>
 struct SmemLayout {
+  static constexpr int kStages = kPair ? kStagesPair : kStagesSingle;
   static constexpr int kBoxBytes = kBlockN * 64 * 2;        // one [128][64] bf16 box
-  static constexpr int kTileBytes = kBoxBytes * (HD / 64);  // one Q / K / V tile
+  static constexpr int kTileBytes = kBoxBytes * (HD / 64);  // one whole Q / K / V tile
+  static constexpr int kKBoxBytes = kPair ? kBoxBytes / 2 : kBoxBytes;   // one box of this CTA's part of a K tile
+  static constexpr int kStageBytes = kPair ? kTileBytes / 2 : kTileBytes;  // this CTA's part of a K or V tile
   static constexpr int kQOff = 0;
   static constexpr int kKOff = kTileBytes;
-  static constexpr int kVOff = kKOff + kStages * kTileBytes;
-  static constexpr int kBarOff = kVOff + kStages * kTileBytes;
+  static constexpr int kVOff = kKOff + kStages * kStageBytes;
+  static constexpr int kBarOff = kVOff + kStages * kStageBytes;
   static constexpr int kNumBars = 1 + 4 * kStages + kSBufs + kSBufs + 2;
-  static constexpr int kMiscOff = kBarOff + kNumBars * 8;      // tmem address + two give-up flags
+  static constexpr int kMiscOff = kBarOff + kNumBars * 8;      // tmem address, two give-up flags, skip flag
   static constexpr int kTotal = kMiscOff + 16;
 };
 
@@ -244,24 +253,44 @@ __device__ __forceinline__ void exp_pass(const uint32_t (&r)[64], uint64_t c2, u
 #define DFS_POLY_GROUPS_D64 8
 #endif
 
-template <int HD, bool kFine>
+// kPair (dense calls, HD = 128): two CTAs on neighbouring SMs, launched as a cluster, take two
+// consecutive query blocks and walk the same key blocks.  Every MMA is one tcgen05.mma.cta_group::2 over
+// 256 query rows issued by the even CTA (the leader): each CTA contributes its own Q tile (or its own P in
+// tensor memory) and receives its own 128 rows of the result in its own tensor memory, and each CTA loads
+// only HALF of every K and V tile, which the tensor cores of both SMs read.  K and V therefore cross from
+// L2 into shared memory once per 256 query rows instead of once per 128.  What changes against the
+// single-CTA form: the TMA loads of both CTAs count on the leader's full barriers; the leader's commits go
+// to the barriers of both CTAs (two commits, one per CTA); the softmax warps of the other CTA arrive on the
+// leader's P barrier through its shared::cluster address (a plain arrive: with cluster-scope release
+// semantics on it every softmax warp lost ~700 cycles per step, and what it publishes, P in tensor memory,
+// is ordered by the tcgen05 fences anyway); set-up and tear-down are cluster-wide barriers.  Everything a
+// softmax warp waits on is a barrier of its own CTA.  Measured against single CTAs on the dense call:
+// 1 239 against 1 200 TFLOP/s in bursts (Wan 480p, 8 heads), 157.6 against 162.5 ms sustained at the
+// HunyuanVideo 720p shape.  Listed (sparse) rows stay single: neighbouring query blocks share only a
+// third of their key blocks.
+template <int HD, bool kFine, bool kPair>
 __global__ void __launch_bounds__(kThreads, 1)
     bsattn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const Params p) {
-  using L = SmemLayout<HD>;
+  static_assert(!kPair || (HD == 128 && !kFine), "pairs: dense calls with 128-wide heads");
+  using L = SmemLayout<HD, kPair>;
+  constexpr int kStages = L::kStages;
   constexpr int kPolyGroups = HD == 128 ? DFS_POLY_GROUPS_D128 : DFS_POLY_GROUPS_D64;
   // D = 128: exponentials against the current reference maximum first, row maxima checked afterwards
   // (one pass in the common case).  D = 64 keeps the separate maximum pass: with half of its exp2 on
   // the FMA pipe the extra max instructions of the fused pass cost more than the pass they save.
   constexpr bool kSpeculate = HD == 128;
   extern __shared__ __align__(1024) uint8_t smem[];
-  if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need 1024-byte alignment
-    if (threadIdx.x == 0 && p.status) atomicExch(p.status, DFS_STATUS_BAD_SMEM_ALIGNMENT);
-    return;
+  const bool misaligned = (smem_u32(smem) & 1023u) != 0;  // the swizzled tiles need 1024-byte alignment
+  if constexpr (!kPair) {
+    if (misaligned) {
+      if (threadIdx.x == 0 && p.status) atomicExch(p.status, DFS_STATUS_BAD_SMEM_ALIGNMENT);
+      return;
+    }
+    // a CTA that starts after another one has given up does no work: one expired wait must not
+    // cost a wait limit per remaining CTA
+    if (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) return;
   }
-  // a CTA that starts after another one has given up does no work: one expired wait must not
-  // cost a wait limit per remaining CTA
-  if (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) return;
   uint8_t* q_tile = smem + L::kQOff;
   uint8_t* k_ring = smem + L::kKOff;
   uint8_t* v_ring = smem + L::kVOff;
@@ -276,11 +305,18 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* mma_drain = p_full + kSBufs;  // [2]  give-up path of the two issuers
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint32_t* skip_flag = tmem_slot + 3;  // pairs only: this CTA would rather not start (see below)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // heavy rows (the dense text rows sit at the end) are scheduled first
-  const int qb = p.q_blocks - 1 - static_cast<int>(blockIdx.x);
+  // pairs: rank of this CTA in its cluster of two; the even one issues the MMAs for both
+  uint32_t rank = 0;
+  if constexpr (kPair) rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  // single CTAs: heavy rows (the dense text rows sit at the end) are scheduled first.  Pairs: CTA r of
+  // pair i takes query block 2 i + r; with an odd number of blocks the last CTA has no rows (its Q tile
+  // reads as zeros and nothing is stored), but it still loads its halves of K and V for its partner.
+  const int qb = kPair ? static_cast<int>(blockIdx.x) : p.q_blocks - 1 - static_cast<int>(blockIdx.x);
   const int head = blockIdx.y;                 // row of the Q/K/V tensors
   const int group = head / p.list_heads;       // batch element
   const int lhead = head - group * p.list_heads;  // head within the batch element: lists and output
@@ -300,50 +336,92 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (int b = 0; b < kSBufs; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&p_full[b], 8);  // one arrival per softmax warp
+      mbar_init(&p_full[b], kPair ? 16 : 8);  // one arrival per softmax warp (of both CTAs of a pair)
     }
     for (int b = 0; b < 2; ++b) mbar_init(&mma_drain[b], 1);
     abort_flag[0] = 0;  // set by the first wait that expires
     abort_flag[1] = 0;  // separate limit for the drain waits of the give-up path
+    if constexpr (kPair)
+      *skip_flag = (misaligned ? 2u : 0u) |
+                   ((p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) ? 1u : 0u);
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, kTmemCols);
-    tmem_relinquish();
+    if constexpr (kPair) {
+      tmem_alloc_pair(tmem_slot, kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (kPair) cluster_sync_all(); else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Pairs: neither CTA may leave while the other still signals its barriers, so "do not start" (a failure
+  // was recorded earlier, or the shared memory is misaligned) is decided together: both CTAs skip their
+  // roles when either of them wants to, and both still go through the common tear-down.
+  bool skip = false;
+  if constexpr (kPair) skip = (*skip_flag | ld_cluster_u32(cluster_addr(skip_flag, rank ^ 1u))) != 0u;
 
-  if (warp == 0) {
+  if (skip) {
+    // pairs only: nothing to do, straight to the tear-down
+  } else if (warp == 0) {
     // ------------------------------ producer ------------------------------
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
-      mbar_arrive_expect_tx(q_full, L::kTileBytes);
-      for (int c = 0; c < HD / 64; ++c)
-        tma_load_3d(q_tile + c * L::kBoxBytes, &tm_q, q_full, c * 64, qb * kBlockM, head);
+      if constexpr (kPair) {
+        // both Q tiles and both halves of every K and V tile are counted on the LEADER's barriers, which
+        // the leader arms with the bytes of the two CTAs together
+        if (leader) mbar_arrive_expect_tx(q_full, 2 * L::kTileBytes);
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_3d_pair(q_tile + c * L::kBoxBytes, &tm_q, cluster_addr(q_full, 0), c * 64, qb * kBlockM, head);
+      } else {
+        mbar_arrive_expect_tx(q_full, L::kTileBytes);
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_3d(q_tile + c * L::kBoxBytes, &tm_q, q_full, c * 64, qb * kBlockM, head);
+      }
       bool ok = true;
       int issued_k = 0, issued_v = 0;
       int s = 0;
       uint32_t ph = 0;
       for (int j = 0; j < n_tiles; ++j) {
         const int kb = my_idx ? __ldg(my_idx + j) : j;
-        ok = mbar_wait_bounded(&k_empty[s], ph ^ 1, abort_flag);  // passes at once in the first round
+        // Pairs: the K ring is as deep as there are score tiles, so "Q.K^T(j) has completed" (the K slot
+        // is free) and "the scores of step j are there" are the same event, and the leader signals it once
+        // per CTA instead of twice (every commit is an idle gap in the issuing thread's stream of MMAs).
+        static_assert(!kPair || kStages == kSBufs, "pairs release K slots through the score barriers");
+        ok = mbar_wait_bounded(kPair ? &s_full[s] : &k_empty[s], ph ^ 1, abort_flag);  // passes at once in the first round
         if (!ok) break;
-        mbar_arrive_expect_tx(&k_full[s], L::kTileBytes);
-        for (int c = 0; c < HD / 64; ++c)
-          tma_load_3d(k_ring + s * L::kTileBytes + c * L::kBoxBytes, &tm_k, &k_full[s], c * 64, kb * kBlockN,
-                      head);
+        if constexpr (kPair) {
+          // this CTA's 64 keys of the tile (all dims): HD / 64 boxes of [64 keys][64 dims]
+          if (leader) mbar_arrive_expect_tx(&k_full[s], L::kTileBytes);
+          for (int c = 0; c < HD / 64; ++c)
+            tma_load_3d_pair(k_ring + s * L::kStageBytes + c * L::kKBoxBytes, &tm_k, cluster_addr(&k_full[s], 0), c * 64,
+                             kb * kBlockN + static_cast<int>(rank) * (kBlockN / 2), head);
+        } else {
+          mbar_arrive_expect_tx(&k_full[s], L::kTileBytes);
+          for (int c = 0; c < HD / 64; ++c)
+            tma_load_3d(k_ring + s * L::kTileBytes + c * L::kBoxBytes, &tm_k, &k_full[s], c * 64, kb * kBlockN,
+                        head);
+        }
         ++issued_k;
         ok = mbar_wait_bounded(&v_empty[s], ph ^ 1, abort_flag);
         if (!ok) break;
-        mbar_arrive_expect_tx(&v_full[s], L::kTileBytes);
-        for (int c = 0; c < HD / 64; ++c)
-          tma_load_3d(v_ring + s * L::kTileBytes + c * L::kBoxBytes, &tm_v, &v_full[s], c * 64, kb * kBlockN,
-                      head);
+        if constexpr (kPair) {
+          // this CTA's 64 dims of the tile (all keys): one box of [128 keys][64 dims]
+          if (leader) mbar_arrive_expect_tx(&v_full[s], L::kTileBytes);
+          tma_load_3d_pair(v_ring + s * L::kStageBytes, &tm_v, cluster_addr(&v_full[s], 0), static_cast<int>(rank) * 64,
+                           kb * kBlockN, head);
+        } else {
+          mbar_arrive_expect_tx(&v_full[s], L::kTileBytes);
+          for (int c = 0; c < HD / 64; ++c)
+            tma_load_3d(v_ring + s * L::kTileBytes + c * L::kBoxBytes, &tm_v, &v_full[s], c * 64, kb * kBlockN,
+                        head);
+        }
         ++issued_v;
         if (++s == kStages) {
           s = 0;
@@ -352,11 +430,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!ok) {
         // drain: the copies already issued must land before the CTA may exit
-        mbar_wait_bounded(q_full, 0, abort_flag + 1);
-        for (int j = issued_k > kStages ? issued_k - kStages : 0; j < issued_k; ++j)
-          mbar_wait_bounded(&k_full[j % kStages], (j / kStages) & 1, abort_flag + 1);
-        for (int j = issued_v > kStages ? issued_v - kStages : 0; j < issued_v; ++j)
-          mbar_wait_bounded(&v_full[j % kStages], (j / kStages) & 1, abort_flag + 1);
+        if (!kPair || leader) {
+          mbar_wait_bounded(q_full, 0, abort_flag + 1);
+          for (int j = issued_k > kStages ? issued_k - kStages : 0; j < issued_k; ++j)
+            mbar_wait_bounded(&k_full[j % kStages], (j / kStages) & 1, abort_flag + 1);
+          for (int j = issued_v > kStages ? issued_v - kStages : 0; j < issued_v; ++j)
+            mbar_wait_bounded(&v_full[j % kStages], (j / kStages) & 1, abort_flag + 1);
+        } else {
+          // the other CTA of a pair has no barrier of its own for its copies (they count on the leader's):
+          // it gives them a millisecond, a thousand times what a copy from L2 or HBM takes
+          const long long t0 = clock64();
+          while (clock64() - t0 < 2000000LL) {
+          }
+        }
       }
     }
   } else if (warp == 1 || warp == 2) {
@@ -368,18 +454,23 @@ __global__ void __launch_bounds__(kThreads, 1)
     // wait there left the pipe idle for the ~300 cycles an MMA group needs to report completion).
     // Two threads because the pipe's issue queue is shallow: the commits and barrier waits of one
     // thread are idle gaps in its stream of MMAs, which the other thread's stream fills.
-    if (lane == 0) {
+    // Pairs: the leader's two threads issue for both CTAs (a third issuing thread changed nothing).
+    constexpr int kIssuers = 2;
+    if (lane == 0 && leader) {
       const int par = warp - 1;
-      constexpr uint32_t idesc_pv = umma_idesc_bf16(kBlockM, HD, 0, 1);
-      constexpr uint32_t idesc_qk = umma_idesc_bf16(kBlockM, kBlockN, 0, 0);
+      // pairs: one instruction covers the 256 query rows of both CTAs
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(kPair ? 2 * kBlockM : kBlockM, HD, 0, 1);
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(kPair ? 2 * kBlockM : kBlockM, kBlockN, 0, 0);
       // Descriptors are built once; per stage and per 16-element step they are one 64-bit add
       // (the start-address field counts 16-byte units).
       // V tile = HD/64 boxes of [128 keys][64 dims], used as an MN-major operand: 16 KB between
       // the 64-wide groups along the head dimension, 1 KB between groups of 8 keys.
+      // Pairs: the descriptors name the same offsets in the shared memory of both CTAs; each CTA's
+      // part of a K tile is [64 keys][HD] (boxes of 8 KB), of a V tile [128 keys][64 dims] (one box).
       const uint64_t v_desc0 = umma_desc_sw128(smem_u32(v_ring), L::kBoxBytes, 1024);
       const uint64_t q_desc = umma_desc_sw128(smem_u32(q_tile), 16, 1024);
       const uint64_t k_desc0 = umma_desc_sw128(smem_u32(k_ring), 16, 1024);
-      constexpr uint64_t kStageStep = L::kTileBytes >> 4;
+      constexpr uint64_t kStageStep = L::kStageBytes >> 4;
       const uint32_t o_tmem = tmem_base + kColO;
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag);
 
@@ -391,18 +482,27 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t d_tmem = tmem_base + s_col(j);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          constexpr uint32_t kBoxStep = L::kBoxBytes >> 4;
-          const uint64_t off = (ks / 4) * kBoxStep + (ks % 4) * 2;  // 32 bytes per 16-element K step
-          umma_ss(d_tmem, q_desc + off, k_desc + off, idesc_qk, ks > 0);
+          // 32 bytes per 16-element step inside a 64-wide box, then the next box
+          const uint64_t q_off = (ks / 4) * (L::kBoxBytes >> 4) + (ks % 4) * 2;
+          const uint64_t k_off = (ks / 4) * (L::kKBoxBytes >> 4) + (ks % 4) * 2;
+          if constexpr (kPair)
+            umma_ss_pair(d_tmem, q_desc + q_off, k_desc + k_off, idesc_qk, ks > 0);
+          else
+            umma_ss(d_tmem, q_desc + q_off, k_desc + k_off, idesc_qk, ks > 0);
         }
-        umma_commit(&k_empty[s]);
-        umma_commit(&s_full[j % kSBufs]);
+        if constexpr (kPair) {
+          umma_commit_pair(smem_u32(&s_full[j % kSBufs]));   // also releases K slot s of this CTA
+          umma_commit_pair(cluster_addr(&s_full[j % kSBufs], 1));
+        } else {
+          umma_commit(&k_empty[s]);
+          umma_commit(&s_full[j % kSBufs]);
+        }
         return true;
       };
 
       // the first three score tiles: 0 and 2 from the even thread, 1 from the odd one
-      for (int j = par; j < kSBufs && j < n_tiles && ok; j += 2) ok = issue_qk(j);
-      for (int j = par; j < n_tiles && ok; j += 2) {
+      for (int j = par; j < kSBufs && j < n_tiles && ok; j += kIssuers) ok = issue_qk(j);
+      for (int j = par; j < n_tiles && ok; j += kIssuers) {
         const int s = j % kStages;
         ok = mbar_wait_bounded(&v_full[s], (j / kStages) & 1, abort_flag);
         if (!ok) break;
@@ -419,16 +519,25 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint64_t v_desc = v_desc0 + kStageStep * s;
         const uint32_t p_tmem = tmem_base + s_col(j);
         // 16 keys per step: 8 packed columns of P, 16 rows (2 KB = 128 address units) of V
-        umma_ts(o_tmem, p_tmem, v_desc, idesc_pv, j > 0);
+        if constexpr (kPair) {
+          umma_ts_pair(o_tmem, p_tmem, v_desc, idesc_pv, j > 0);
 #pragma unroll
-        for (int ks = 1; ks < kBlockN / 16; ++ks)
-          umma_ts(o_tmem, p_tmem + ks * 8, v_desc + static_cast<uint64_t>(ks * 128), idesc_pv, 1);
-        umma_commit(&v_empty[s]);
+          for (int ks = 1; ks < kBlockN / 16; ++ks)
+            umma_ts_pair(o_tmem, p_tmem + ks * 8, v_desc + static_cast<uint64_t>(ks * 128), idesc_pv, 1);
+          umma_commit_pair(smem_u32(&v_empty[s]));
+          umma_commit_pair(cluster_addr(&v_empty[s], 1));
+        } else {
+          umma_ts(o_tmem, p_tmem, v_desc, idesc_pv, j > 0);
+#pragma unroll
+          for (int ks = 1; ks < kBlockN / 16; ++ks)
+            umma_ts(o_tmem, p_tmem + ks * 8, v_desc + static_cast<uint64_t>(ks * 128), idesc_pv, 1);
+          umma_commit(&v_empty[s]);
+        }
         if (j + kSBufs < n_tiles) ok = issue_qk(j + kSBufs);
       }
       if (!ok) {
         // give-up path: let the MMAs already issued finish before TMEM is freed
-        umma_commit(&mma_drain[par]);
+        if constexpr (kPair) umma_commit_pair(smem_u32(&mma_drain[par])); else umma_commit(&mma_drain[par]);
         mbar_wait_bounded(&mma_drain[par], 0, abort_flag + 1);
       }
     }
@@ -443,7 +552,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int lane_base = quad * 32 + sub * 16;
     const uint32_t lane_sel = static_cast<uint32_t>(lane_base) << 16;
     const int t4 = lane & 3;
-    const int row_a = lane_base + (lane >> 2), row_b = row_a + 8;  // rows of the tile
+    const int row_a = lane_base + (lane >> 2);  // first of this thread's two rows of the tile (the other: + 8)
     const float c = p.scale_log2;
     const uint64_t c2 = pack2(c, c);
     float m_a = -INFINITY, m_b = -INFINITY;  // reference maxima (raw score units) of the two rows
@@ -483,7 +592,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&p_full[j % kSBufs]);
+        if (lane == 0) mbar_arrive(&p_full[j % kSBufs]);   // (tile maps: never a pair)
         continue;
       }
       uint32_t r[64];
@@ -587,7 +696,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[j % kSBufs]);
+      if (lane == 0) {
+        // pairs: the P barrier that counts is the leader's (sixteen warps arrive on it)
+        if (kPair && !leader) mbar_arrive_cluster(cluster_addr(&p_full[j % kSBufs], 0)); else mbar_arrive(&p_full[j % kSBufs]);
+      }
     }
 
     // row sums: this thread's columns, then the row's four threads
@@ -652,13 +764,18 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 
   // ------------------------------- tear-down -------------------------------
+  // pairs: a cluster-wide barrier, so that neither CTA frees its tensor memory or leaves while the
+  // other one may still signal its barriers or have an MMA running on it
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (kPair) cluster_sync_all(); else __syncthreads();
   if (abort_flag[0] != 0 && threadIdx.x == 0 && p.status) atomicExch(p.status, DFS_STATUS_WAIT_TIMEOUT);
+  if constexpr (kPair) {
+    if (misaligned && threadIdx.x == 0 && p.status) atomicExch(p.status, DFS_STATUS_BAD_SMEM_ALIGNMENT);
+  }
   if (warp == 1) {
     __syncwarp();
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (kPair) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -667,19 +784,52 @@ __global__ void __launch_bounds__(kThreads, 1)
 // --------------------------------------------------------------------------
 // [H, L, D] bf16 as a 3-D tensor (D innermost), box = 64 x 128 x 1, 128-byte swizzle,
 // rows past L read as zero.
-int make_tile_map(CUtensorMap* map, const void* base, int heads, int64_t seq_len, int head_dim) {
-  return dfs_make_bf16_tile_map(map, base, heads, seq_len, head_dim);
+int make_tile_map(CUtensorMap* map, const void* base, int heads, int64_t seq_len, int head_dim,
+                  int box_rows = 128) {
+  return dfs_make_bf16_tile_map(map, base, heads, seq_len, head_dim, box_rows);
 }
 
 template <int HD, bool kFine>
 int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int heads,
                cudaStream_t stream) {
-  using L = SmemLayout<HD>;
-  DFS_CUDA_CHECK(cudaFuncSetAttribute(bsattn_fwd_kernel<HD, kFine>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      L::kTotal));
+  using L = SmemLayout<HD, false>;
+  DFS_CUDA_CHECK(cudaFuncSetAttribute(bsattn_fwd_kernel<HD, kFine, false>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
   dim3 grid(p.q_blocks, heads);
-  bsattn_fwd_kernel<HD, kFine><<<grid, kThreads, L::kTotal, stream>>>(mq, mk, mv, p);
+  bsattn_fwd_kernel<HD, kFine, false><<<grid, kThreads, L::kTotal, stream>>>(mq, mk, mv, p);
   return static_cast<int>(cudaGetLastError());
+}
+
+// Dense call with 128-wide heads: clusters of two CTAs, each pair on two consecutive query blocks
+// (mk: K with boxes of 64 rows, the half tile one CTA loads).
+int launch_fwd_pairs(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int heads,
+                     cudaStream_t stream) {
+  using L = SmemLayout<128, true>;
+  auto kernel = bsattn_fwd_kernel<128, false, true>;
+  DFS_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>((p.q_blocks + 1) / 2 * 2), static_cast<unsigned>(heads), 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = L::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  DFS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, mq, mk, mv, p));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Whether dense calls with 128-wide heads run as CTA pairs.
+bool dense_pairs_enabled() {
+  static const int flag = [] {
+    const char* e = getenv("DFSATTN_DENSE_PAIRS");
+    return e == nullptr ? 1 : (e[0] != '0');
+  }();
+  return flag != 0;
 }
 
 }  // namespace
@@ -722,9 +872,10 @@ int block_sparse_fwd_impl(const void* q, const void* k, const void* v, const int
   if (!(scale > 0.f)) return DFS_ERR_RANGE;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
 
+  const bool pairs = idx == nullptr && head_dim == 128 && dense_pairs_enabled();
   CUtensorMap mq, mk, mv;
   int rc = make_tile_map(&mq, q, all_heads, seq_len, head_dim);
-  if (rc == 0) rc = make_tile_map(&mk, k, all_heads, seq_len, head_dim);
+  if (rc == 0) rc = make_tile_map(&mk, k, all_heads, seq_len, head_dim, pairs ? 64 : 128);
   if (rc == 0) rc = make_tile_map(&mv, v, all_heads, seq_len, head_dim);
   if (rc != 0) return rc;
 
@@ -751,6 +902,7 @@ int block_sparse_fwd_impl(const void* q, const void* k, const void* v, const int
   p.q_blocks = static_cast<int>((seq_len + kBlockM - 1) / kBlockM);
   p.k_blocks = static_cast<int>((kv_len + kBlockN - 1) / kBlockN);
   p.scale_log2 = scale * 1.4426950408889634f;
+  if (pairs) return launch_fwd_pairs(mq, mk, mv, p, all_heads, stream);
   if (fine != nullptr)
     return head_dim == 128 ? launch_fwd<128, true>(mq, mk, mv, p, all_heads, stream)
                            : launch_fwd<64, true>(mq, mk, mv, p, all_heads, stream);

@@ -174,11 +174,13 @@ __global__ void __launch_bounds__(256) pool_tiles_kernel(const T* __restrict__ q
 // One CTA per (128 pooled query rows, head, range of key tiles); it walks its 128-column tiles of pooled keys.
 //   warp 0   TMA producer: Q hi/lo once, K hi/lo tiles through a 2-stage ring
 //   warp 1   MMA issuer (one lane): 3 x D/16 MMAs per column tile into one of two TMEM buffers
-//   warps 2-5 epilogue: one thread per pooled query row reads the 128 logits (tcgen05.ld) and
-//            reduces each group of 8 (one key block) to a base-2 log-sum-exp
+//   warps 2-9 epilogue: one thread per pooled query row and half of the 128 logits of a column tile
+//            (two warps share a TMEM lane quadrant and take two of its four 32-column groups each, so a
+//            scheduler has two warps to cover each other's tcgen05.ld latency); each group of 8 logits
+//            (one key block) is reduced to a base-2 log-sum-exp
 // Every wait is bounded; an expired wait sets *status and the CTA leaves through the common tear-down.
 // --------------------------------------------------------------------------
-constexpr int kLseThreads = 192;
+constexpr int kLseThreads = 320;
 constexpr int kLseStages = 2;
 
 template <int HD>
@@ -246,7 +248,7 @@ __global__ void __launch_bounds__(kLseThreads, 1)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&s_empty[b], 4);  // one arrival per epilogue warp
+      mbar_init(&s_empty[b], 8);  // one arrival per epilogue warp
     }
     mbar_init(mma_drain, 1);
     abort_flag[0] = 0;
@@ -324,6 +326,7 @@ __global__ void __launch_bounds__(kLseThreads, 1)
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;   // which two of the four 32-column groups of a tile
     const int row = row0 + quad * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
     float* __restrict__ out_row = lse + (static_cast<size_t>(head) * s.nq + (row < s.nq ? row : 0)) * s.k_blocks;
@@ -333,18 +336,21 @@ __global__ void __launch_bounds__(kLseThreads, 1)
       ok = mbar_wait_bounded(&s_full[b], (ct >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
+      // both 32-column groups of this warp are requested before either is used
+      uint32_t r[2][32];
+      tmem_ld32(tmem_base + lane_sel + b * 128 + (2 * half) * 32, r[0]);
+      tmem_ld32(tmem_base + lane_sel + b * 128 + (2 * half + 1) * 32, r[1]);
+      tmem_wait_ld();
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + lane_sel + b * 128 + g * 32, r);
-        tmem_wait_ld();
+      for (int gg = 0; gg < 2; ++gg) {
+        const int g = 2 * half + gg;
 #pragma unroll
         for (int grp = 0; grp < 32 / TPB; ++grp) {  // one key block = TPB consecutive pooled columns
           float v[TPB];
           float m = -INFINITY;
 #pragma unroll
           for (int i = 0; i < TPB; ++i) {
-            v[i] = __uint_as_float(r[grp * TPB + i]) * scale_log2;
+            v[i] = __uint_as_float(r[gg][grp * TPB + i]) * scale_log2;
             m = fmaxf(m, v[i]);
           }
           float sum = 0.f;
