@@ -53,6 +53,7 @@ SIGNATURES = {
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int,
                                 c_void_p]),
     "dfs_selftest_wait_timeout": (c_int, [c_int64, c_void_p, c_void_p]),
+    "dfs_status_snapshot": (c_int, [c_void_p, c_void_p, c_void_p]),
 }
 
 

@@ -929,6 +929,19 @@ __global__ void wait_timeout_selftest_kernel(int32_t* status, long long limit_cy
 }
 }  // namespace
 
+namespace {
+__global__ void status_snapshot_kernel(const int32_t* __restrict__ status, volatile int32_t* mirror) {
+  *mirror = *reinterpret_cast<const volatile int32_t*>(status);
+  __threadfence_system();
+}
+}  // namespace
+
+extern "C" int dfs_status_snapshot(const int32_t* status, int32_t* mirror, void* stream) {
+  if (status == nullptr || mirror == nullptr) return DFS_ERR_NULL;
+  status_snapshot_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(status, mirror);
+  return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" int dfs_selftest_wait_timeout(int64_t limit_cycles, int32_t* status, void* stream) {
   if (status == nullptr) return DFS_ERR_NULL;
   if (limit_cycles < 1 || limit_cycles >= (1LL << 31)) return DFS_ERR_RANGE;

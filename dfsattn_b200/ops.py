@@ -75,7 +75,7 @@ def check_status(device=None):
 def poll_status(device):
     """Called at the start of every operator call: look at the copy of the status word that the
     PREVIOUS call queued (if that copy has finished; no wait otherwise), raise ``RuntimeError`` and
-    clear the word if it was set, then queue a fresh asynchronous copy into pinned host memory
+    clear the word if it was set, then queue a fresh snapshot into pinned host memory
     behind the work already on the current stream.  A give-up is therefore reported one call late
     at the latest once the stream has drained, and without any synchronisation on the fast path."""
     key = _device_key(device)
@@ -92,7 +92,10 @@ def poll_status(device):
             mon["host"][0] = 0
             _raise_status(word, code)
     if mon["event"] is None:
-        mon["host"].copy_(word, non_blocking=True)
+        # a one-thread kernel writes the word into the pinned host int: unlike a copy it does not queue
+        # behind the large transfers a DMA engine may be busy with for other streams
+        check(lib.dfs_status_snapshot(word.data_ptr(), mon["host"].data_ptr(), _stream(torch.device("cuda", key))),
+              "dfs_status_snapshot")
         ev = torch.cuda.Event()
         ev.record(torch.cuda.current_stream(torch.device("cuda", key)))
         mon["event"] = ev

@@ -304,6 +304,13 @@ int dfs_block_sparse_fwd_batched(const void* q, const void* k, const void* v, co
 
 /* ---- diagnostics ----------------------------------------------------------- */
 
+/* Copies the status word to *mirror behind the work already queued on `stream`, with a one-thread
+ * kernel.  mirror is any address the device can write: device memory, or page-locked host memory
+ * (with unified addressing its host pointer is the device pointer), which the host can then poll
+ * without synchronising and without putting a copy into the queue of a DMA engine, where it would
+ * wait behind large transfers of other streams.  No counterpart in the reference. */
+int dfs_status_snapshot(const int32_t* status, int32_t* mirror, void* stream);
+
 /* Exercises the give-up path of the kernels' bounded waits without any other work: one small
  * CTA waits, for at most limit_cycles SM clock cycles, on a barrier that nothing ever completes,
  * then leaves through the same tear-down as the attention kernel and writes
