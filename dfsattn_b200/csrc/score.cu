@@ -43,6 +43,7 @@ struct ScoreShape {
   int k_blocks;
   int nq, nk;          // pooled tiles (q_blocks*8, k_blocks*8)
   int nq_pad, nk_pad;  // padded to kGemmTile
+  int lse_stride;      // floats per row of the stored log-sum-exps: key blocks rounded up to whole column tiles
   long long video_padded;  // Vb*128: scoring position where the text part starts
 };
 
@@ -62,13 +63,15 @@ __host__ ScoreShape make_shape(int heads, int64_t seq_len, int64_t video_len, in
   s.nq_pad = (s.nq + kGemmTile - 1) / kGemmTile * kGemmTile;
   s.nk_pad = (s.nk + kGemmTile - 1) / kGemmTile * kGemmTile;
   s.video_padded = static_cast<long long>(s.q_blocks) * kBlock;
+  s.lse_stride = s.nk_pad / s.tpb;
   return s;
 }
 
 __host__ size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 
 // scratch layout: pooled Q as bf16 [2H][nq_pad][D] (plane 2h = hi, 2h+1 = lo), pooled K likewise,
-// then the per-(query tile, key block) log-sum-exp values fp32 [H][nq][Kb]
+// then the per-(query tile, key block) log-sum-exp values fp32 [H][nq][lse_stride] (rows padded to whole
+// column tiles, so that a thread stores its consecutive key blocks of a tile as aligned 16-byte vectors)
 struct Workspace {
   size_t qm_off, km_off, lse_off, total;
 };
@@ -77,7 +80,7 @@ __host__ Workspace make_workspace(const ScoreShape& s) {
   w.qm_off = 0;
   w.km_off = align256(w.qm_off + 2 * sizeof(__nv_bfloat16) * s.heads * s.head_dim * static_cast<size_t>(s.nq_pad));
   w.lse_off = align256(w.km_off + 2 * sizeof(__nv_bfloat16) * s.heads * s.head_dim * static_cast<size_t>(s.nk_pad));
-  w.total = align256(w.lse_off + sizeof(float) * s.heads * static_cast<size_t>(s.nq) * s.k_blocks);
+  w.total = align256(w.lse_off + sizeof(float) * s.heads * static_cast<size_t>(s.nq) * s.lse_stride);
   return w;
 }
 
@@ -329,7 +332,7 @@ __global__ void __launch_bounds__(kLseThreads, 1)
     const int half = (warp - 2) >> 2;   // which two of the four 32-column groups of a tile
     const int row = row0 + quad * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
-    float* __restrict__ out_row = lse + (static_cast<size_t>(head) * s.nq + (row < s.nq ? row : 0)) * s.k_blocks;
+    float* __restrict__ out_row = lse + (static_cast<size_t>(head) * s.nq + (row < s.nq ? row : 0)) * s.lse_stride;
     bool ok = true;
     for (int ct = 0; ct < n_ct; ++ct) {
       const int b = ct & 1;
@@ -344,6 +347,7 @@ __global__ void __launch_bounds__(kLseThreads, 1)
 #pragma unroll
       for (int gg = 0; gg < 2; ++gg) {
         const int g = 2 * half + gg;
+        float res[32 / TPB];   // this thread's consecutive key blocks of the 32-column group
 #pragma unroll
         for (int grp = 0; grp < 32 / TPB; ++grp) {  // one key block = TPB consecutive pooled columns
           float v[TPB];
@@ -356,8 +360,16 @@ __global__ void __launch_bounds__(kLseThreads, 1)
           float sum = 0.f;
 #pragma unroll
           for (int i = 0; i < TPB; ++i) sum += ex2_approx(v[i] - m);
-          const int kb = (ct0 + ct) * (kGemmTile / TPB) + g * (32 / TPB) + grp;
-          if (row < s.nq && kb < s.k_blocks) out_row[kb] = m + lg2_approx(sum);
+          res[grp] = m + lg2_approx(sum);
+        }
+        // whole 16-byte vectors: a row is padded to whole column tiles (key blocks past the last one hold
+        // the value of all-zero pooled keys and are never read)
+        const int kb0 = (ct0 + ct) * (kGemmTile / TPB) + g * (32 / TPB);
+        if (row < s.nq) {
+#pragma unroll
+          for (int q4 = 0; q4 < 32 / TPB / 4; ++q4)
+            *reinterpret_cast<float4*>(out_row + kb0 + 4 * q4) =
+                make_float4(res[4 * q4], res[4 * q4 + 1], res[4 * q4 + 2], res[4 * q4 + 3]);
         }
       }
       tc_fence_before_sync();
@@ -384,9 +396,9 @@ __global__ void __launch_bounds__(256) block_sum_kernel(const float* __restrict_
   const int head = blockIdx.y;
   const int qb = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const float* __restrict__ rows = lse + (static_cast<size_t>(head) * s.nq + qb * s.tpb) * s.k_blocks;
+  const float* __restrict__ rows = lse + (static_cast<size_t>(head) * s.nq + qb * s.tpb) * s.lse_stride;
   if (warp < s.tpb) {
-    const float* __restrict__ r = rows + static_cast<size_t>(warp) * s.k_blocks;  // warp i <-> pooled row i
+    const float* __restrict__ r = rows + static_cast<size_t>(warp) * s.lse_stride;  // warp i <-> pooled row i
     float m = -INFINITY;
     for (int c = lane; c < s.k_blocks; c += 32) m = fmaxf(m, r[c]);
 #pragma unroll
@@ -405,7 +417,7 @@ __global__ void __launch_bounds__(256) block_sum_kernel(const float* __restrict_
   for (int c = threadIdx.x; c < s.k_blocks; c += blockDim.x) {
     float b = 0.f;
     for (int i = 0; i < s.tpb; ++i)
-      b += exp2f(rows[static_cast<size_t>(i) * s.k_blocks + c] - row_max[i]) * row_inv[i];
+      b += exp2f(rows[static_cast<size_t>(i) * s.lse_stride + c] - row_max[i]) * row_inv[i];
     out[c] = b;
   }
 }
@@ -551,7 +563,7 @@ fine_top_p_kernel(const __nv_bfloat16* __restrict__ qm, const __nv_bfloat16* __r
   }
   // normaliser of each of the 8 pooled query rows over ALL key tiles: log2 sum_c 2^lse[i][c]
   {
-    const float* __restrict__ r = lse + (static_cast<size_t>(head) * s.nq + qb * 8 + warp) * s.k_blocks;
+    const float* __restrict__ r = lse + (static_cast<size_t>(head) * s.nq + qb * 8 + warp) * s.lse_stride;
     float m = -INFINITY;
     for (int c = lane; c < s.k_blocks; c += 32) m = fmaxf(m, r[c]);
 #pragma unroll
