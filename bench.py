@@ -526,10 +526,10 @@ def run_trace(args, spec, rank, local_rank, world):
             "warmup": args.warmup, "ms_per_step": 1e3 * secs, "ms_x_mhz": cycles, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
             "clocks": clocks,
-            # dense call: the attention kernel; cached: permute + attention; refresh: + pool, tile scores,
-            # normalisers and selection
-            "gpu_launches": args.steps * sum(v["calls_per_trace"] * (1 if k == "dense" else 6 if
-                                             k.startswith("refresh") else 2) for k, v in table.items()),
+            # every call: status snapshot; dense call: + the attention kernel; cached: + permute + attention;
+            # refresh: + pool, tile scores, block sums and selection
+            "gpu_launches": args.steps * sum(v["calls_per_trace"] * (2 if k == "dense" else 7 if
+                                             k.startswith("refresh") else 3) for k, v in table.items()),
             "calls_ms": table,
             "roofline": {"bound": "tensor", "kernel": "bsattn_fwd_kernel<128>", "achieved": value / world,
                          "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
@@ -946,7 +946,7 @@ def run_gpu(args, spec, rank, local_rank, world):
             "config": config,
             "clocks": clocks,
             "e2e": e2e,
-            "gpu_launches": 6 * args.steps,
+            "gpu_launches": 7 * args.steps,   # status snapshot, permute, pool, tile scores, block sums, selection, attention
             "stages": stages,
             "roofline": {"bound": "tensor", "kernel": "bsattn_fwd_kernel<128>", "achieved": attn_tflops,
                          "peak": peak, "unit": "TFLOP/s", "frac": attn_tflops / peak,
