@@ -17,7 +17,9 @@
  *  - `stream` is a cudaStream_t passed as void*.  No call synchronises and none
  *    allocates device memory.  State kept between calls: host-side lookups that
  *    are made once (the driver's tensor-map encoder, the per-device address of
- *    the fixed scratch array of dfs_block_scores_static); nothing else.
+ *    the fixed scratch array of dfs_block_scores_static, the environment switch
+ *    DFSATTN_DENSE_PAIRS: "0" runs dense calls on single CTAs instead of CTA
+ *    pairs); nothing else.
  *  - Kernels never trap: every wait inside a kernel is bounded; a kernel that
  *    gives up writes a non-zero code to `*status` (device int32, caller
  *    zero-initialised, may be NULL for kernels that have no waits).  The word
@@ -231,7 +233,8 @@ int dfs_select_topk(const float* scores, int heads, int score_rows, int q_rows, 
  * Replaces block_sparse_attn_func(..., base_blockmask, ...) as called at
  * dfsattn/attention_hyvideo.py:1075-1082 and attention_wan.py:379-386, and,
  * with idx == NULL (every key block), flash_attn_varlen_func at
- * dfsattn/fullattention.py:108-116.
+ * dfsattn/fullattention.py:108-116 (with D = 128 that dense call runs as
+ * clusters of two CTAs sharing every K and V tile; same results).
  *  q, k, v : bf16 [H, L, D], already permuted; D = 64 or 128.
  *  idx/cnt : int32 [H, Qb, kmax] / [H, Qb] ascending block lists (Qb = ceil(L/128));
  *            cnt = -1 marks a row that attends every key block (its list is not read).
