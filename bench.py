@@ -82,22 +82,22 @@ class ClockSampler:
         except Exception:
             return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
 
-    def _poll_nvml(self):
+    def _sample_nvml(self):
         nv, h = self.nvml
-        bits = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
-                "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
-                "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
-                "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
-        mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+        bits = (nv.nvmlClocksEventReasonHwSlowdown, nv.nvmlClocksEventReasonHwThermalSlowdown,
+                nv.nvmlClocksEventReasonSwThermalSlowdown, nv.nvmlClocksEventReasonSwPowerCap)
+        try:
+            sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+            mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            pw = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+            mask = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+            self.rows.append([str(sm), str(mx), str(pw)] + ["Active" if mask & bit else "Not Active" for bit in bits])
+        except Exception:
+            pass
+
+    def _poll_nvml(self):
         while not self._stop.is_set():
-            try:
-                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
-                pw = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
-                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
-                self.rows.append([str(sm), str(mx), str(pw)] +
-                                 ["Active" if mask & bit else "Not Active" for bit in bits.values()])
-            except Exception:
-                pass
+            self._sample_nvml()
             self._stop.wait(0.01)
 
     def start(self):
@@ -125,6 +125,8 @@ class ClockSampler:
         if self.nvml is not None:
             self._stop.set()
             self.thread.join(timeout=2)
+            if not self.rows:   # a timed region shorter than the polling thread's start-up: one sample right after it
+                self._sample_nvml()
         elif self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         else:

@@ -34,10 +34,15 @@ def test_call_workload_line():
     assert {"permute_ms", "score_select_ms", "attention_ms", "fused_prepare_ms"} <= set(d["stages"])
     assert "sm_mhz" in d["clocks"] and "reasons" in d["clocks"]
     assert d["stages"]["kp_attention_ms"] > 0 and 0 < d["stages"]["kp_tiles_kept_frac"] <= 1
+    assert d["stages"]["dense_attention_ms"] > 0 and d["ms_x_mhz"] > 0
+    e = d["e2e"]
+    assert e["copy_only_ms"] > 0 and e["h2d_gbs_per_gpu"] > 0 and e["floor_ms"] >= e["copy_only_ms"]
+    # the other configurations ride in the same line: five Wan calls and the 1-layer trace
+    assert len(d["configs"]) == 6 and all(v.get("tflops", 0) > 0 for v in d["configs"].values()), d["configs"]
 
 
 def test_wan_workload_line_times_the_guidance_pair():
-    d = _run("--workload", "tiny_wan", "--steps", "3", "--warmup", "3", "--cpu-blocks", "4")
+    d = _run("--workload", "tiny_wan", "--steps", "3", "--warmup", "3", "--cpu-blocks", "4", "--no-extras")
     assert d["value"] > 0 and d["config"]["workload"] == "tiny_wan"
     assert d["stages"]["cfg_two_calls_ms"] > 0 and d["stages"]["cfg_pair_call_ms"] > 0
 
@@ -51,4 +56,5 @@ def test_trace_workload_line():
     assert calls["dense"]["calls_per_trace"] == 24
     assert sum(v["calls_per_trace"] for k, v in calls.items() if k.startswith("refresh")) == 8
     assert sum(v["calls_per_trace"] for k, v in calls.items() if k.startswith("cached")) == 68
-    assert d["gpu_launches"] == 24 * 1 + 8 * 6 + 68 * 2
+    # per call one status snapshot; dense: + attention; cached: + permute + attention; refresh: + four scoring kernels
+    assert d["gpu_launches"] == 24 * 2 + 8 * 7 + 68 * 3 and d["ms_x_mhz"] > 0
