@@ -4,7 +4,8 @@
 // One CTA per (query block, head), 12 warps:
 //   warp 0      TMA producer: the Q tile once, then the K and V tiles of every
 //               listed key block into two 3-stage shared-memory rings
-//               (full/empty mbarrier per stage).
+//               (full/empty mbarrier per stage; a K slot is released by the barrier that
+//               announces its scores).
 //   warps 1, 2  MMA issuers (one lane each), warp 1 for the even steps, warp 2 for the
 //               odd ones.  For its step j a thread issues O += P(j) V(j)
 //               (tcgen05.mma TS form: P read from TMEM, V as MN-major B operand)
@@ -77,7 +78,7 @@ struct SmemLayout {
   static constexpr int kKOff = kTileBytes;
   static constexpr int kVOff = kKOff + kStages * kStageBytes;
   static constexpr int kBarOff = kVOff + kStages * kStageBytes;
-  static constexpr int kNumBars = 1 + 4 * kStages + kSBufs + kSBufs + 2;
+  static constexpr int kNumBars = 1 + 3 * kStages + kSBufs + kSBufs + 2;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;      // tmem address, two give-up flags, skip flag
   static constexpr int kTotal = kMiscOff + 16;
 };
@@ -297,10 +298,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;            // [3]  TMA -> Q.K^T issuer
-  uint64_t* k_empty = k_full + kStages;   // [3]  Q.K^T(j) completed: K slot j%3 is free
-  uint64_t* v_full = k_empty + kStages;   // [3]  TMA -> P.V issuer
+  uint64_t* v_full = k_full + kStages;    // [3]  TMA -> P.V issuer
   uint64_t* v_empty = v_full + kStages;   // [3]  P.V(j) completed: V slot j%3 is free and O holds step j
-  uint64_t* s_full = v_empty + kStages;   // [3]  Q.K^T issuer -> softmax: scores of step j are in S[j%3]
+  uint64_t* s_full = v_empty + kStages;   // [3]  Q.K^T issuer -> softmax: scores of step j are in S[j%3] (and K slot j%3 is free)
   uint64_t* p_full = s_full + kSBufs;     // [3]  softmax -> P.V issuer: P(j) is in the first half of S[j%3]
   uint64_t* mma_drain = p_full + kSBufs;  // [2]  give-up path of the two issuers
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
@@ -330,7 +330,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_init(q_full, 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&k_full[s], 1);
-      mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
     }
@@ -390,11 +389,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t ph = 0;
       for (int j = 0; j < n_tiles; ++j) {
         const int kb = my_idx ? __ldg(my_idx + j) : j;
-        // Pairs: the K ring is as deep as there are score tiles, so "Q.K^T(j) has completed" (the K slot
-        // is free) and "the scores of step j are there" are the same event, and the leader signals it once
-        // per CTA instead of twice (every commit is an idle gap in the issuing thread's stream of MMAs).
-        static_assert(!kPair || kStages == kSBufs, "pairs release K slots through the score barriers");
-        ok = mbar_wait_bounded(kPair ? &s_full[s] : &k_empty[s], ph ^ 1, abort_flag);  // passes at once in the first round
+        // The K ring is as deep as there are score tiles, so "Q.K^T(j) has completed" (the K slot is
+        // free) and "the scores of step j are there" are the same event: one commit signals both (every
+        // commit is an idle gap in the issuing thread's stream of MMAs).
+        static_assert(kStages == kSBufs, "K slots are released through the score barriers");
+        ok = mbar_wait_bounded(&s_full[s], ph ^ 1, abort_flag);  // passes at once in the first round
         if (!ok) break;
         if constexpr (kPair) {
           // this CTA's 64 keys of the tile (all dims): HD / 64 boxes of [64 keys][64 dims]
@@ -494,8 +493,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           umma_commit_pair(smem_u32(&s_full[j % kSBufs]));   // also releases K slot s of this CTA
           umma_commit_pair(cluster_addr(&s_full[j % kSBufs], 1));
         } else {
-          umma_commit(&k_empty[s]);
-          umma_commit(&s_full[j % kSBufs]);
+          umma_commit(&s_full[j % kSBufs]);   // also releases K slot s
         }
         return true;
       };
@@ -504,17 +502,22 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int j = par; j < kSBufs && j < n_tiles && ok; j += kIssuers) ok = issue_qk(j);
       for (int j = par; j < n_tiles && ok; j += kIssuers) {
         const int s = j % kStages;
+        // What this step needs besides P(j) -- V(j) and the completion of P.V(j-1) -- is waited for FIRST: it
+        // normally is there long before the softmax warps are done, and a barrier wait costs ~100 cycles even
+        // when it passes at once, cycles that would otherwise sit between the arrival of P and the first MMA.
+        // (Not so the K tile of the Q.K^T that follows: the producer requests it only after V(j+2), i.e.
+        // after P.V(j-1) has completed, and waiting for it here would put its latency in front of P.V(j).)
         ok = mbar_wait_bounded(&v_full[s], (j / kStages) & 1, abort_flag);
-        if (!ok) break;
-        ok = mbar_wait_bounded(&p_full[j % kSBufs], (j / kSBufs) & 1, abort_flag);
         if (!ok) break;
         if (j > 0) {
           // O += P(j) V(j) follows P.V(j-1), which the other thread issued: wait until that one
-          // has completed (it was issued a step ago; its barrier's next phase is P.V(j+2), issued
-          // by this thread later on, so the parity wait cannot be fooled).
+          // has completed (its barrier's next phase is P.V(j+2), issued by this thread later on, so the
+          // parity wait cannot be fooled).
           ok = mbar_wait_bounded(&v_empty[(j - 1) % kStages], ((j - 1) / kStages) & 1, abort_flag);
           if (!ok) break;
         }
+        ok = mbar_wait_bounded(&p_full[j % kSBufs], (j / kSBufs) & 1, abort_flag);
+        if (!ok) break;
         tc_fence_after_sync();
         const uint64_t v_desc = v_desc0 + kStageStep * s;
         const uint32_t p_tmem = tmem_base + s_col(j);
