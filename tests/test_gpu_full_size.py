@@ -80,6 +80,25 @@ def test_sampled_rows_against_fp32_arithmetic(full):
         assert m["max_abs"] <= 2e-2 and m["cosine"] >= 0.9999, m
 
 
+def test_dense_call_at_full_size(full):
+    """The dense call of the warm-up steps on the full shape (466 CTA pairs per head; the last pair has
+    one CTA without rows): softmax mass one on every row, sampled rows against fp32 arithmetic."""
+    from dfsattn_b200.fullattention import full_attention
+    q, k, v = full["q"], full["k"], full["v"]
+    ones = full_attention(q, k, torch.ones_like(v), mode="flash")
+    assert float((ones.float() - 1).abs().max()) <= 1e-2
+    del ones
+    out = full_attention(q, k, v, mode="flash")
+    torch.cuda.synchronize()
+    full["ops"].check_status("cuda")
+    rows = torch.cat([torch.arange(3, L, 7001, device="cuda"), torch.arange(L - 260, L, 41, device="cuda")])
+    for head in (0, 11, 23):
+        s = (q[0, head, rows].float() @ k[0, head].float().T) * D ** -0.5
+        want = torch.softmax(s, -1) @ v[0, head].float()
+        m = oracle.tensor_metrics(out[0, head, rows].float().cpu(), want.cpu())
+        assert m["max_abs"] <= 2e-2 and m["cosine"] >= 0.9999, m
+
+
 def test_permute_round_trip_is_the_identity(full):
     ops = full["ops"]
     perm, inv = oracle.build_permutation(full["vperm"], L, VIDEO)
