@@ -25,12 +25,12 @@
 //               maxima and sums are two shuffles and no warp depends on another).
 //               Per step: load the scores, exp2 in the log2 domain with packed
 //               fp32x2 arithmetic against the current reference maximum of the
-//               row while the tile's row maxima are gathered in the same pass,
-//               P as packed bf16 over the first half of the score buffer it
-//               came from (tcgen05.st shape 16x128b).  The reference maximum
-//               moves, and O is rescaled in TMEM, only when a row maximum grew by
-//               more than 2^8 (then the tile is read again and redone); sum and P
-//               use the same reference maximum, so the result is exact.
+//               row (no maxima of the tile itself are taken), P as packed bf16
+//               over the first half of the score buffer it came from (tcgen05.st
+//               shape 16x128b).  The reference maximum moves, and O is rescaled in
+//               TMEM, only when a partial row sum shows that some score lies 2^60
+//               above it (then the tile is read again and redone); sum and P use
+//               the same reference maximum, so the result is exact.
 //               Epilogue: normalise, store bf16 rows, optionally through a row
 //               map (fused inverse permutation).
 //   warp 3      idle (keeps the softmax warps aligned to TMEM lane quadrants).
@@ -62,7 +62,12 @@ constexpr uint32_t kTmemCols = 512;
 constexpr int kSBufs = 3;
 constexpr uint32_t kColO = 384;
 __device__ __forceinline__ uint32_t s_col(int j) { return static_cast<uint32_t>(j % kSBufs) * 128u; }
-constexpr float kRescaleThreshold = 8.0f;  // log2 units
+// The softmax takes its exponentials against the row's current reference maximum without looking at the tile's
+// own maximum first.  The reference only has to keep the exponentials inside the range of fp32 and bf16 (both
+// reach 2^127; relative precision does not depend on the scale), so it is moved only when a thread's partial
+// row sum of the tile exceeds this bound (or is not finite): then some score lies far above the reference,
+// and the tile is redone with the separate maximum pass.  A sum below the bound means every exponential is.
+constexpr float kSumBound = 1.0e18f;  // ~2^60: room for 2^17 keys times 2^60 below 2^127
 
 // kPair: the CTA is one of a pair that shares every K and V tile (see the pair notes at the kernel).
 // It then holds HALF of each: 64 of the 128 keys of a K tile (all dims: boxes of [64 rows][64 bf16]) and 64
@@ -185,16 +190,15 @@ __device__ __forceinline__ void mask_tail(uint32_t (&r)[64], int valid, int t4) 
 }
 
 // One pass over a thread's share of a score tile (two rows a and b): P = exp2(S*c - m*c) packed as
-// bf16 pairs (P column 4i + t of a row = keys 8i + 2t, 8i + 2t + 1), the tile's partial row sums,
-// and with kTrackMax the thread's share of the tile's raw row maxima.  The first kPoly groups take
-// their exponentials on the FMA pipe.  With kFine, key tile t (columns 16t .. 16t + 15: groups 2t and
-// 2t + 1) takes part only if bit t of `keep` is set; the 16 rows of a softmax warp are one query
-// tile, so the test is uniform over the warp and a dropped tile costs two stores of zero.
-template <int kPoly, bool kTrackMax, bool kFine>
+// bf16 pairs (P column 4i + t of a row = keys 8i + 2t, 8i + 2t + 1) and the tile's partial row sums.
+// The first kPoly groups take their exponentials on the FMA pipe.  With kFine, key tile t (columns
+// 16t .. 16t + 15: groups 2t and 2t + 1) takes part only if bit t of `keep` is set; the 16 rows of a
+// softmax warp are one query tile, so the test is uniform over the warp and a dropped tile costs two
+// stores of zero.
+template <int kPoly, bool kFine>
 __device__ __forceinline__ void exp_pass(const uint32_t (&r)[64], uint64_t c2, uint64_t nma2, uint64_t nmb2,
                                          uint32_t (&packed)[32], uint64_t& ta0, uint64_t& ta1, uint64_t& tb0,
-                                         uint64_t& tb1, float& mt_a, float& mt_b, uint32_t keep) {
-  float xa0 = -INFINITY, xa1 = -INFINITY, xb0 = -INFINITY, xb1 = -INFINITY;
+                                         uint64_t& tb1, uint32_t keep) {
   ta0 = ta1 = tb0 = tb1 = pack2(0.f, 0.f);
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
@@ -204,15 +208,6 @@ __device__ __forceinline__ void exp_pass(const uint32_t (&r)[64], uint64_t c2, u
     }
     const float sa0 = __uint_as_float(r[4 * i]), sa1 = __uint_as_float(r[4 * i + 1]);
     const float sb0 = __uint_as_float(r[4 * i + 2]), sb1 = __uint_as_float(r[4 * i + 3]);
-    if (kTrackMax) {
-      if (i & 1) {
-        xa1 = max3(xa1, sa0, sa1);
-        xb1 = max3(xb1, sb0, sb1);
-      } else {
-        xa0 = max3(xa0, sa0, sa1);
-        xb0 = max3(xb0, sb0, sb1);
-      }
-    }
     const uint64_t xa = fma2(pack2(sa0, sa1), c2, nma2);
     const uint64_t xb = fma2(pack2(sb0, sb1), c2, nmb2);
     float a0, a1, b0, b1;
@@ -237,21 +232,16 @@ __device__ __forceinline__ void exp_pass(const uint32_t (&r)[64], uint64_t c2, u
     packed[2 * i] = cvt_bf16x2(a0, a1);      // row a (even key in the low half)
     packed[2 * i + 1] = cvt_bf16x2(b0, b1);  // row b
   }
-  if (kTrackMax) {
-    mt_a = fmaxf(xa0, xa1);
-    mt_b = fmaxf(xb0, xb1);
-  }
 }
 
 // Of the 16 column groups of a score tile, how many have their exp2 evaluated by the polynomial
-// on the FMA pipe instead of the special-function unit.  Measured: half of them for D = 64, where
-// the tensor work per tile is smaller and the special-function unit is the tighter limit; two of
-// them for D = 128 (the issue slots of the softmax warps are the next limit: 3 and 4 gain less).
+// on the FMA pipe instead of the special-function unit.  Measured (same box): 2 for D = 128 (1, 3 and 4
+// are 1-2 % slower); 3 for D = 64 (2 to 5 within 2 %, 6 and 8 slower).
 #ifndef DFS_POLY_GROUPS_D128
 #define DFS_POLY_GROUPS_D128 2
 #endif
 #ifndef DFS_POLY_GROUPS_D64
-#define DFS_POLY_GROUPS_D64 8
+#define DFS_POLY_GROUPS_D64 3
 #endif
 
 // kPair (dense calls, HD = 128): two CTAs on neighbouring SMs, launched as a cluster, take two
@@ -277,10 +267,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   using L = SmemLayout<HD, kPair>;
   constexpr int kStages = L::kStages;
   constexpr int kPolyGroups = HD == 128 ? DFS_POLY_GROUPS_D128 : DFS_POLY_GROUPS_D64;
-  // D = 128: exponentials against the current reference maximum first, row maxima checked afterwards
-  // (one pass in the common case).  D = 64 keeps the separate maximum pass: with half of its exp2 on
-  // the FMA pipe the extra max instructions of the fused pass cost more than the pass they save.
-  constexpr bool kSpeculate = HD == 128;
   extern __shared__ __align__(1024) uint8_t smem[];
   const bool misaligned = (smem_u32(smem) & 1023u) != 0;  // the swizzled tiles need 1024-byte alignment
   if constexpr (!kPair) {
@@ -603,23 +589,37 @@ __global__ void __launch_bounds__(kThreads, 1)
       tmem_wait_ld();
       if (valid < kBlockN) mask_tail(r, valid, t4);
 
-      // The reference maximum of a row moves only when a tile exceeds it by more than the
-      // threshold, which is rare after the first tile.  So the exponentials are taken against the
-      // current reference straight away and the tile's row maxima are gathered in the same pass
-      // (max on the ALU while the special-function unit is the busy one); only when some row of the
-      // warp did exceed the threshold is the tile read again and redone against the new reference.
+      // After the first tile the exponentials are taken against the row's current reference maximum straight
+      // away, without the tile's own maxima (no max instructions and no shuffles in the common case); only
+      // when a partial row sum shows that some score lies far above the reference (kSumBound), or a row
+      // that had no reference yet sees its first keys, is the tile read again, its maxima found, the
+      // reference moved (O rescaled in tensor memory) and the pass redone.  Sum and P always use the same
+      // reference, so the result is exact.
       uint32_t packed[32];
       uint64_t ta0, ta1, tb0, tb1;  // this tile's partial row sums
-      float mt_a = -INFINITY, mt_b = -INFINITY;
-      bool redo = true;  // the exp2 pass against the final reference is still to be done
-      if (kSpeculate && j > 0) {
+      bool redo = true;             // the exp2 pass against the final reference is still to be done
+      if (j > 0) {
         // a row may still be without a reference (-inf): every key it has seen so far was dropped by a
-        // tile map or lies past kv_len; the redo below then settles it
+        // tile map or lies past kv_len
         const float nma = (m_a == -INFINITY) ? 0.f : -m_a * c;
         const float nmb = (m_b == -INFINITY) ? 0.f : -m_b * c;
-        exp_pass<kPolyGroups, true, kFine>(r, c2, pack2(nma, nma), pack2(nmb, nmb), packed, ta0, ta1, tb0, tb1, mt_a,
-                                           mt_b, keep);
-      } else {
+        exp_pass<kPolyGroups, kFine>(r, c2, pack2(nma, nma), pack2(nmb, nmb), packed, ta0, ta1, tb0, tb1, keep);
+        // did any exponential leave the safe range?  (!(x <= bound) also catches inf and NaN)
+        float sa0, sa1, sb0, sb1;
+        unpack2(add2(ta0, ta1), sa0, sa1);
+        unpack2(add2(tb0, tb1), sb0, sb1);
+        const float pa = sa0 + sa1, pb = sb0 + sb1;
+        const bool grow = !(pa <= kSumBound) || !(pb <= kSumBound) || (m_a == -INFINITY && pa > 0.f) ||
+                          (m_b == -INFINITY && pb > 0.f);
+        redo = __any_sync(0xffffffffu, grow) != 0;
+        if (redo) {   // rare: read the tile again
+          tmem_ld_16x256b_x16(s_addr, r);
+          tmem_wait_ld();
+          if (valid < kBlockN) mask_tail(r, valid, t4);
+        }
+      }
+      if (redo) {
+        // the tile's row maxima: this thread's columns, then the row's four threads
         float xa0 = -INFINITY, xa1 = -INFINITY, xb0 = -INFINITY, xb1 = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {
@@ -629,29 +629,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           xa1 = max3(xa1, __uint_as_float(r[4 * i + 4]), __uint_as_float(r[4 * i + 5]));
           xb1 = max3(xb1, __uint_as_float(r[4 * i + 6]), __uint_as_float(r[4 * i + 7]));
         }
-        mt_a = fmaxf(xa0, xa1);
-        mt_b = fmaxf(xb0, xb1);
-      }
-      mt_a = fmaxf(mt_a, __shfl_xor_sync(0xffffffffu, mt_a, 1));
-      mt_b = fmaxf(mt_b, __shfl_xor_sync(0xffffffffu, mt_b, 1));
-      mt_a = fmaxf(mt_a, __shfl_xor_sync(0xffffffffu, mt_a, 2));
-      mt_b = fmaxf(mt_b, __shfl_xor_sync(0xffffffffu, mt_b, 2));
-      bool moved = true;  // some row of the warp needs a new reference (always so in the first tile)
-      if constexpr (!kSpeculate) {
-        const bool grow = (mt_a - m_a) * c > kRescaleThreshold || (mt_b - m_b) * c > kRescaleThreshold;
-        moved = __any_sync(0xffffffffu, grow) != 0;
-      }
-      if (kSpeculate && j > 0) {
-        const bool grow = (mt_a - m_a) * c > kRescaleThreshold || (mt_b - m_b) * c > kRescaleThreshold;
-        redo = __any_sync(0xffffffffu, grow) != 0;
-        if (redo) {
-          tmem_ld_16x256b_x16(s_addr, r);
-          tmem_wait_ld();
-          if (valid < kBlockN) mask_tail(r, valid, t4);
-        }
-      }
-      if (redo) {
-       if (kSpeculate || moved) {
+        float mt_a = fmaxf(xa0, xa1), mt_b = fmaxf(xb0, xb1);
+        mt_a = fmaxf(mt_a, __shfl_xor_sync(0xffffffffu, mt_a, 1));
+        mt_b = fmaxf(mt_b, __shfl_xor_sync(0xffffffffu, mt_b, 1));
+        mt_a = fmaxf(mt_a, __shfl_xor_sync(0xffffffffu, mt_a, 2));
+        mt_b = fmaxf(mt_b, __shfl_xor_sync(0xffffffffu, mt_b, 2));
         const float na = fmaxf(m_a, mt_a), nb = fmaxf(m_b, mt_b);
         const float alpha_a = (m_a == -INFINITY) ? 0.f : ex2((m_a - na) * c);
         const float alpha_b = (m_b == -INFINITY) ? 0.f : ex2((m_b - nb) * c);
@@ -683,12 +665,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             tmem_st_16x256b_x8(o_addr + h * 64, o);
           }
         }
-       }
         // a row whose keys are all masked keeps the reference -inf: its exponentials are exp2(-inf) = 0
         const float nma = (m_a == -INFINITY) ? 0.f : -m_a * c, nmb = (m_b == -INFINITY) ? 0.f : -m_b * c;
-        float unused_a, unused_b;
-        exp_pass<kPolyGroups, false, kFine>(r, c2, pack2(nma, nma), pack2(nmb, nmb), packed, ta0, ta1, tb0, tb1,
-                                            unused_a, unused_b, keep);
+        exp_pass<kPolyGroups, kFine>(r, c2, pack2(nma, nma), pack2(nmb, nmb), packed, ta0, ta1, tb0, tb1, keep);
       }
       // only now: the scores are not needed any more
       tmem_st_16x128b_x16(p_addr, packed);

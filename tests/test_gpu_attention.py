@@ -127,6 +127,32 @@ def test_large_magnitude_scores_exercise_the_rescale_path(ops):
     _close(_run(ops, q, k, v, perm, None), want)
 
 
+@pytest.mark.parametrize("jump", [40.0, 400.0, 4000.0])
+def test_scores_far_above_the_reference_move_it(ops, jump):
+    """The D = 128 softmax takes its exponentials against the reference maximum of the first tile and moves
+    it only when a partial row sum leaves the safe range.  Keys whose scores lie `jump` (raw units, i.e.
+    jump * 0.128 in log2 units after scaling) above everything before them: below the bound (exponentials
+    up to 2^5 times the reference), above it (2^51 ... and, accumulated over a tile, past the bound), and
+    far beyond the range of fp32 (inf in the first pass).  Dense and listed rows, every row against SDPA."""
+    g = torch.Generator().manual_seed(int(jump))
+    H, L, D = 2, 128 * 5, 128
+    q = torch.randn(1, H, L, D, generator=g)
+    k = torch.randn(1, H, L, D, generator=g) * 0.1
+    v = torch.randn(1, H, L, D, generator=g)
+    u = torch.nn.functional.normalize(q.mean(dim=2, keepdim=True), dim=-1)       # a direction most queries like
+    q = q + 4 * u
+    late = slice(128 * 3 + 17, 128 * 3 + 40)                                      # a few keys in the fourth tile
+    k[:, :, late] = k[:, :, late] + u * (jump / 4)                                # q.k grows by about `jump`
+    perm, inv = oracle.build_permutation(None, L)
+    qr, kr, vr = (t.bfloat16().float() for t in (q, k, v))
+    want = torch.nn.functional.scaled_dot_product_attention(qr, kr, vr)
+    _close(_run(ops, q, k, v, perm, None), want)                                  # dense call (CTA pairs)
+    full = torch.ones(H, 5, 5, dtype=torch.bool)
+    _close(_run(ops, q, k, v, perm, full), want)                                  # the same through lists
+    torch.cuda.synchronize()
+    ops.check_status("cuda")
+
+
 def test_padded_tail_is_an_independent_segment(ops):
     # reference analogue: tests/test_flashinfer64_attention.py:565-607
     from dfsattn_b200 import engine
