@@ -14,7 +14,8 @@
 //                          log-sum-exp of the 8 scaled logits of that block is
 //                          kept  (H * Nq * Kb floats).
 //   3. block_sum_kernel  : per query block, row max / normaliser over all key
-//                          blocks from the stored LSEs, then
+//                          blocks from the stored LSEs (read once, held in
+//                          registers), then
 //                          B[c] = sum_i 2^(lse_ic - M_i) / Z_i   (= the sum of
 //                          the 64 softmax-ed tile scores of the 8x8 group).
 // Sums of softmax-ed scores equal the reference's fp32 results up to rounding
@@ -389,8 +390,77 @@ __global__ void __launch_bounds__(kLseThreads, 1)
 }
 
 // One CTA per (query block, head): its pooled rows (at most 8) x Kb stored base-2 LSEs -> Kb block scores.
+// Warp i holds pooled row i in registers (up to kSumVecs 16-byte vectors per lane, all loads in flight at
+// once), so the array is read from memory exactly once: row maximum and normaliser by warp shuffles, the
+// normalised exponentials to shared memory, then one thread per key block adds the rows' contributions.
+constexpr int kSumVecs = 8;                        // rows of up to 32 * 4 * kSumVecs = 1024 key blocks
+constexpr int kSumRowMax = 32 * 4 * kSumVecs;
+
 __global__ void __launch_bounds__(256) block_sum_kernel(const float* __restrict__ lse,
                                                         float* __restrict__ block_scores, ScoreShape s) {
+  extern __shared__ float4 part4[];  // [tpb][lse_stride / 4]: 2^(lse - M_i) / Z_i
+  const int head = blockIdx.y;
+  const int qb = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = s.lse_stride >> 2;  // lse_stride is a multiple of 16 floats
+  if (warp < s.tpb) {
+    const float4* __restrict__ r = reinterpret_cast<const float4*>(
+        lse + (static_cast<size_t>(head) * s.nq + qb * s.tpb + warp) * s.lse_stride);
+    float4 v[kSumVecs];
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kSumVecs; ++j)
+      if (j * 32 < nvec) {  // uniform over the warp: vectors past the row's end cost nothing
+        const int at = j * 32 + lane;
+        v[j] = at < nvec ? __ldcs(r + at) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+#pragma unroll
+    for (int j = 0; j < kSumVecs; ++j)
+      if (j * 32 < nvec) {
+        const int c = (j * 32 + lane) * 4;
+        if (c + 3 >= s.k_blocks) {  // the row's last vectors: columns past the last key block hold nothing defined
+          if (c + 0 >= s.k_blocks) v[j].x = -INFINITY;
+          if (c + 1 >= s.k_blocks) v[j].y = -INFINITY;
+          if (c + 2 >= s.k_blocks) v[j].z = -INFINITY;
+          v[j].w = -INFINITY;
+        }
+        m = fmaxf(m, fmaxf(fmaxf(v[j].x, v[j].y), fmaxf(v[j].z, v[j].w)));
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float z = 0.f;
+#pragma unroll
+    for (int j = 0; j < kSumVecs; ++j)
+      if (j * 32 < nvec) {
+        v[j].x = ex2_approx(v[j].x - m);
+        v[j].y = ex2_approx(v[j].y - m);
+        v[j].z = ex2_approx(v[j].z - m);
+        v[j].w = ex2_approx(v[j].w - m);
+        z += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
+    const float inv = 1.0f / z;
+    float4* dst = part4 + static_cast<size_t>(warp) * nvec;
+#pragma unroll
+    for (int j = 0; j < kSumVecs; ++j) {
+      const int at = j * 32 + lane;
+      if (at < nvec) dst[at] = make_float4(v[j].x * inv, v[j].y * inv, v[j].z * inv, v[j].w * inv);
+    }
+  }
+  __syncthreads();
+  const float* part = reinterpret_cast<const float*>(part4);
+  float* __restrict__ out = block_scores + (static_cast<size_t>(head) * s.q_blocks + qb) * s.k_blocks;
+  for (int c = threadIdx.x; c < s.k_blocks; c += blockDim.x) {
+    float b = 0.f;
+    for (int i = 0; i < s.tpb; ++i) b += part[static_cast<size_t>(i) * s.lse_stride + c];
+    out[c] = b;
+  }
+}
+
+// The same for rows of more than kSumRowMax key blocks: three passes over the stored values.
+__global__ void __launch_bounds__(256) block_sum_long_kernel(const float* __restrict__ lse,
+                                                             float* __restrict__ block_scores, ScoreShape s) {
   __shared__ float row_max[8];
   __shared__ float row_inv[8];
   const int head = blockIdx.y;
@@ -489,7 +559,10 @@ int run_block_scores(const void* q_perm, const void* k_perm, int dtype, const Sc
                        : launch_lse<64, 2>(qm, km, lse, s, scale_log2, status, stream);
   if (err != 0) return err;
   dim3 grid(s.q_blocks, s.heads);
-  block_sum_kernel<<<grid, 256, 0, stream>>>(lse, block_scores, s);
+  if (s.lse_stride <= kSumRowMax)
+    block_sum_kernel<<<grid, 256, sizeof(float) * s.tpb * s.lse_stride, stream>>>(lse, block_scores, s);
+  else
+    block_sum_long_kernel<<<grid, 256, 0, stream>>>(lse, block_scores, s);
   return static_cast<int>(cudaGetLastError());
 }
 

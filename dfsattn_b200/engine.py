@@ -165,9 +165,8 @@ def topk_block_num(sparsity: float, k_blocks: int) -> int:
     return max(1, int(float(sparsity) * k_blocks))
 
 
-def select_lists(scores: torch.Tensor, seq_len: int, video_len: int, sparsity: float,
-                 flavor: str, want_mask: bool = False, kp: bool = False):
-    """Index lists from fp32 block scores with the reference's budget rules.
+def list_budget(seq_len: int, video_len: int, sparsity: float, flavor: str, kp: bool = False):
+    """(n_rank, k_select, dense_row_start) of a selection under the reference's budget rules.
 
     flavor "hyvideo": dfsattn/attention_hyvideo.py:424-443,491-501 (text and
     boundary key blocks use up budget and are always on; rows from the first
@@ -177,8 +176,7 @@ def select_lists(scores: torch.Tensor, seq_len: int, video_len: int, sparsity: f
     kb = math.ceil(seq_len / BLOCK)
     kk = topk_block_num(sparsity, kb)
     if flavor == "wan":
-        return ops.select_topk(scores, q_rows=kb, n_rank=kb, k_select=kk, dense_row_start=kb,
-                               want_mask=want_mask)
+        return kb, kk, kb
     dense_start = video_len // BLOCK
     n_text_blocks = max(0, kb - dense_start)
     text_len = seq_len - video_len
@@ -191,7 +189,14 @@ def select_lists(scores: torch.Tensor, seq_len: int, video_len: int, sparsity: f
         n_sel, n_rank = kk, kb
     # the kp selector keeps every row from the boundary block on dense, text or not (:298-301)
     dense_row_start = dense_start if (text_len > 0 or (kp and n_text_blocks > 0)) else kb
-    return ops.select_topk(scores, q_rows=kb, n_rank=n_rank, k_select=n_sel,
+    return n_rank, n_sel, dense_row_start
+
+
+def select_lists(scores: torch.Tensor, seq_len: int, video_len: int, sparsity: float,
+                 flavor: str, want_mask: bool = False, kp: bool = False):
+    """Index lists from fp32 block scores with the budget of ``list_budget``."""
+    n_rank, n_sel, dense_row_start = list_budget(seq_len, video_len, sparsity, flavor, kp)
+    return ops.select_topk(scores, q_rows=math.ceil(seq_len / BLOCK), n_rank=n_rank, k_select=n_sel,
                            dense_row_start=dense_row_start, want_mask=want_mask)
 
 

@@ -69,6 +69,8 @@ def _select_oracle(scores, n_rank, k_select, dense_row_start, q_rows):
     (3, 8, 10, 10, 7, 2, 7),            # text tail: forced columns + dense rows
     (2, 30, 30, 300, 300, 90, 30),      # more columns than one chunk of threads
     (1, 929, 931, 931, 928, 276, 928),  # 720p HunyuanVideo geometry
+    (1, 40, 40, 600, 590, 100, 38),     # 16 keys per lane
+    (1, 20, 20, 1100, 1090, 250, 20),   # rows past 1024 ranked columns: keys in shared memory
     (2, 6, 6, 6, 6, 6, 6),              # k == all
     (2, 6, 6, 6, 5, 1, 6),              # ragged video, no text: forced last column, no dense rows
 ])
@@ -112,6 +114,24 @@ def test_select_ties_go_to_the_lowest_column(ops):
     scores = torch.tensor([[[1.0, 3.0, 3.0, 2.0, 3.0, 0.5]]])
     idx, cnt, _ = ops.select_topk(scores.cuda(), q_rows=1, n_rank=6, k_select=2, dense_row_start=1)
     assert idx.cpu()[0, 0].tolist() == [1, 2] and int(cnt) == 2
+
+
+@pytest.mark.parametrize("cols", [200, 500, 1000, 1100])
+def test_select_many_ties_every_row_length(ops, cols):
+    """Scores with a handful of distinct values (the k-th place always falls inside a run of equal
+    scores), for each way the kernel holds a row: 8, 16 or 32 keys per lane, or shared memory."""
+    g = torch.Generator().manual_seed(cols)
+    scores = torch.randint(0, 5, (2, 12, cols), generator=g).float() - 2.0      # negative, zero and positive
+    n_rank, k = cols - 3, cols // 3
+    idx, cnt, mask = ops.select_topk(scores.cuda(), q_rows=12, n_rank=n_rank, k_select=k, dense_row_start=12,
+                                     want_mask=True)
+    order = torch.sort(scores[..., :n_rank], dim=-1, descending=True, stable=True).indices[..., :k]
+    want = torch.zeros(2, 12, cols, dtype=torch.bool)
+    want.scatter_(-1, order, True)
+    want[..., n_rank:] = True
+    assert torch.equal(mask.cpu().bool(), want)
+    widx, wcnt = oracle.mask_to_index_lists(want)
+    assert torch.equal(cnt.cpu(), wcnt) and torch.equal(idx.cpu(), widx[..., :idx.shape[-1]])
 
 
 def test_select_rejects_bad_arguments(ops):
@@ -196,6 +216,21 @@ def test_block_scores_other_tile_sizes(ops, name, tile):
     lists = engine.compute_block_lists(qp, kp, video_len, spec["sparsity"], "hyvideo", tile=tile)
     assert_masks_equal_up_to_near_ties(lists.to_bool_mask().cpu(), q.float(), k.float(), perm, video_len,
                                        spec["sparsity"], "hyvideo", tile=tile)
+
+
+@pytest.mark.parametrize("blocks", [1024, 1030])
+def test_block_scores_rows_around_1024_key_blocks(ops, blocks):
+    """The block-sum kernel holds a pooled row of up to 1024 key blocks in registers and falls back to a
+    three-pass kernel past that: both sides of the switch against the oracle."""
+    g = torch.Generator().manual_seed(blocks)
+    L = blocks * 128 - 50
+    q = torch.randn(1, 1, L, 64, generator=g)
+    k = torch.randn(1, 1, L, 64, generator=g) * 2
+    got = ops.block_scores(q[0].cuda(), k[0].cuda(), L, True).cpu()
+    want = oracle.block_scores_wan(q, k, torch.arange(L))[0]
+    torch.testing.assert_close(got, want, rtol=2e-4, atol=1e-6)
+    torch.cuda.synchronize()
+    ops.check_status("cuda")
 
 
 def test_block_scores_rejects_bad_shapes(ops):
