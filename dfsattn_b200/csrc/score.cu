@@ -146,12 +146,26 @@ __global__ void __launch_bounds__(256) pool_tiles_kernel(const T* __restrict__ q
   for (int i = 0; i < E; ++i) acc[i] = 0.f;
   if (tile < n_tiles) {
     const long long p0 = static_cast<long long>(tile) * s.tile;
-#pragma unroll 4
-    for (int r = 0; r < s.tile; ++r) {
-      const long long row = scoring_row(p0 + r, s.video_len, s.video_padded, s.seq_len);
-      if (row >= 0) {
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + row * s.head_dim) + ch);
-        Vec16<T>::accumulate(raw, acc);
+    const long long first = scoring_row(p0, s.video_len, s.video_padded, s.seq_len);
+    const long long last = scoring_row(p0 + s.tile - 1, s.video_len, s.video_padded, s.seq_len);
+    if (first >= 0 && last == first + s.tile - 1) {
+      // the tile lies wholly inside the video or the text part (all but a handful do): its rows are
+      // consecutive, four loads in flight per thread
+      const uint4* __restrict__ base = reinterpret_cast<const uint4*>(src + first * s.head_dim) + ch;
+      for (int r0 = 0; r0 < s.tile; r0 += 4) {  // the tile size is a multiple of 16
+        uint4 raw[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) raw[r] = __ldcs(base + static_cast<size_t>(r0 + r) * chunks);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) Vec16<T>::accumulate(raw[r], acc);
+      }
+    } else {  // a tile across the end of the video or of the text: row by row, skipping the zero rows
+      for (int r = 0; r < s.tile; ++r) {
+        const long long row = scoring_row(p0 + r, s.video_len, s.video_padded, s.seq_len);
+        if (row >= 0) {
+          const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + row * s.head_dim) + ch);
+          Vec16<T>::accumulate(raw, acc);
+        }
       }
     }
   }
