@@ -21,6 +21,7 @@
 // Sums of softmax-ed scores equal the reference's fp32 results up to rounding
 // (different summation order, 2^-16 operand split).
 #include <math.h>
+#include <stdlib.h>
 
 #include <atomic>
 
@@ -190,27 +191,34 @@ __global__ void __launch_bounds__(256) pool_tiles_kernel(const T* __restrict__ q
 // pooled logits on tcgen05 + per-block log-sum-exp epilogue
 //
 // One CTA per (128 pooled query rows, head, range of key tiles); it walks its 128-column tiles of pooled keys.
-//   warp 0   TMA producer: Q hi/lo once, K hi/lo tiles through a 2-stage ring
-//   warp 1   MMA issuer (one lane): 3 x D/16 MMAs per column tile into one of two TMEM buffers
+//   warp 0   TMA producer: Q hi/lo once, K hi/lo tiles through a ring (2 stages; 4 half-size stages in pairs)
+//   warps 1, 10  MMA issuers (one lane each, even / odd column tiles): 3 x D/16 MMAs per column tile into
+//            one of four logits buffers in tensor memory (the epilogue frees a buffer as soon as it has
+//            the logits in registers)
 //   warps 2-9 epilogue: one thread per pooled query row and half of the 128 logits of a column tile
 //            (two warps share a TMEM lane quadrant and take two of its four 32-column groups each, so a
 //            scheduler has two warps to cover each other's tcgen05.ld latency); each group of 8 logits
 //            (one key block) is reduced to a base-2 log-sum-exp
 // Every wait is bounded; an expired wait sets *status and the CTA leaves through the common tear-down.
 // --------------------------------------------------------------------------
-constexpr int kLseThreads = 320;
-constexpr int kLseStages = 2;
+constexpr int kLseThreads = 352;
+constexpr int kLseIssuerB = 10;  // warp of the second MMA issuer
+constexpr int kLseBufs = 4;      // logits buffers in tensor memory (128 columns each: all 512)
 
-template <int HD>
+// kPair: the CTA is one of a pair that shares every pooled-K tile (see the pair notes at the kernel).
+template <int HD, bool kPair>
 struct LseSmem {
+  static constexpr int kStages = kPair ? 4 : 2;
   static constexpr int kBoxBytes = 128 * 64 * 2;
   static constexpr int kTileBytes = kBoxBytes * (HD / 64);   // one 128-row bf16 tile (hi or lo)
+  static constexpr int kKBoxBytes = kPair ? kBoxBytes / 2 : kBoxBytes;     // one box of this CTA's part of a K tile
+  static constexpr int kKPartBytes = kPair ? kTileBytes / 2 : kTileBytes;  // this CTA's part of a K tile (hi or lo)
   static constexpr int kQOff = 0;                            // hi, lo
   static constexpr int kKOff = 2 * kTileBytes;               // [stage][hi, lo]
-  static constexpr int kBarOff = kKOff + kLseStages * 2 * kTileBytes;
-  static constexpr int kNumBars = 1 + 2 * kLseStages + 2 + 2 + 1;
+  static constexpr int kBarOff = kKOff + kStages * 2 * kKPartBytes;
+  static constexpr int kNumBars = 1 + 2 * kStages + 2 * kLseBufs + 2;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
-  static constexpr int kTotal = kMiscOff + 16;
+  static constexpr int kTotal = kMiscOff + 32;
 };
 
 __device__ __forceinline__ float lg2_approx(float x) {
@@ -224,32 +232,50 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-template <int HD, int TPB>
+// kPair: two CTAs on neighbouring SMs, launched as a cluster, take two consecutive 128-row tiles of pooled
+// queries and walk the same pooled-key tiles.  Every MMA is one tcgen05.mma.cta_group::2 over 256 query rows
+// issued by the even CTA (the leader); each CTA keeps its own Q tiles and its own 128 rows of the logits and
+// loads only HALF (64 pooled keys) of every K tile, which the tensor cores of both SMs read.  The pooled keys
+// therefore cross from L2 into shared memory once per 256 query rows instead of once per 128: with single
+// CTAs this kernel is bound by exactly that traffic (64 KB per 128 x 128 logits).  The loads of both CTAs
+// count on the leader's full barriers, the leader's commits go to the barriers of both CTAs, the epilogue
+// warps of the other CTA release a logits buffer on the leader's barrier through its shared::cluster address,
+// set-up and tear-down are cluster-wide barriers.
+template <int HD, int TPB, bool kPair>
 __global__ void __launch_bounds__(kLseThreads, 1)
     tile_lse_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     float* __restrict__ lse, ScoreShape s, float scale_log2, int32_t* status) {
-  using L = LseSmem<HD>;
+  using L = LseSmem<HD, kPair>;
+  constexpr int kStages = L::kStages;
   extern __shared__ __align__(1024) uint8_t smem[];
-  if ((smem_u32(smem) & 1023u) != 0) {
-    if (threadIdx.x == 0 && status) atomicExch(status, DFS_STATUS_BAD_SMEM_ALIGNMENT);
-    return;
+  const bool misaligned = (smem_u32(smem) & 1023u) != 0;
+  if constexpr (!kPair) {
+    if (misaligned) {
+      if (threadIdx.x == 0 && status) atomicExch(status, DFS_STATUS_BAD_SMEM_ALIGNMENT);
+      return;
+    }
+    if (status != nullptr && *reinterpret_cast<volatile int32_t*>(status) != 0) return;
   }
-  if (status != nullptr && *reinterpret_cast<volatile int32_t*>(status) != 0) return;
   uint8_t* q_tiles = smem + L::kQOff;
   uint8_t* k_ring = smem + L::kKOff;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;               // [2]
-  uint64_t* k_empty = k_full + kLseStages;   // [2]
-  uint64_t* s_full = k_empty + kLseStages;   // [2]  logits of a column tile are in TMEM buffer b
-  uint64_t* s_empty = s_full + 2;            // [2]  the epilogue has read buffer b
-  uint64_t* mma_drain = s_empty + 2;
+  uint64_t* k_full = bars + 1;            // [stages]
+  uint64_t* k_empty = k_full + kStages;   // [stages]
+  uint64_t* s_full = k_empty + kStages;   // [bufs]  logits of a column tile are in TMEM buffer b
+  uint64_t* s_empty = s_full + kLseBufs;  // [bufs]  the epilogue has read buffer b
+  uint64_t* mma_drain = s_empty + kLseBufs;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile uint32_t* skip_flag = tmem_slot + 3;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // pairs: rank of this CTA in its cluster of two; the even one issues the MMAs for both
+  uint32_t rank = 0;
+  if constexpr (kPair) rank = cluster_ctarank();
+  const bool leader = rank == 0;
   const int head = blockIdx.y;
-  const int row0 = blockIdx.x * kGemmTile;
+  const int row0 = blockIdx.x * kGemmTile;  // pairs: rows past the padded pooled queries read as zeros
   // Column tiles of this CTA: the key tiles are cut into gridDim.z contiguous ranges (every (query tile,
   // key block) value is independent of the others, so small head counts still fill the GPU).  `ct`
   // below counts this CTA's tiles from zero (ring stages and barrier phases); ct0 + ct is the tile.
@@ -260,86 +286,149 @@ __global__ void __launch_bounds__(kLseThreads, 1)
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < kLseStages; ++i) {
+    for (int i = 0; i < kStages; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kLseBufs; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&s_empty[b], 8);  // one arrival per epilogue warp
+      mbar_init(&s_empty[b], kPair ? 16 : 8);  // one arrival per epilogue warp (of both CTAs of a pair)
     }
-    mbar_init(mma_drain, 1);
+    mbar_init(&mma_drain[0], 1);
+    mbar_init(&mma_drain[1], 1);
     abort_flag[0] = 0;
     abort_flag[1] = 0;
+    if constexpr (kPair)
+      *skip_flag = (misaligned ? 2u : 0u) |
+                   ((status != nullptr && *reinterpret_cast<volatile int32_t*>(status) != 0) ? 1u : 0u);
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 256);
-    tmem_relinquish();
+    if constexpr (kPair) {
+      tmem_alloc_pair(tmem_slot, 128 * kLseBufs);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, 128 * kLseBufs);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (kPair) cluster_sync_all(); else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Pairs: neither CTA may leave while the other still signals its barriers, so "do not start" is decided
+  // together: both CTAs skip their roles when either of them wants to, and both go through the tear-down.
+  bool skip = false;
+  if constexpr (kPair)
+    skip = (*skip_flag | ld_cluster_u32(cluster_addr(const_cast<uint32_t*>(skip_flag), rank ^ 1u))) != 0u;
 
-  if (warp == 0) {
+  if (skip) {
+    // pairs only: nothing to do, straight to the tear-down
+  } else if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
-      mbar_arrive_expect_tx(q_full, 2 * L::kTileBytes);
-      for (int part = 0; part < 2; ++part)
-        for (int c = 0; c < HD / 64; ++c)
-          tma_load_3d(q_tiles + part * L::kTileBytes + c * L::kBoxBytes, &tm_q, q_full, c * 64, row0,
-                      2 * head + part);
+      if constexpr (kPair) {
+        // the Q tiles of both CTAs and both halves of every K tile are counted on the LEADER's barriers,
+        // which the leader arms with the bytes of the two CTAs together
+        if (leader) mbar_arrive_expect_tx(q_full, 2 * 2 * L::kTileBytes);
+        for (int part = 0; part < 2; ++part)
+          for (int c = 0; c < HD / 64; ++c)
+            tma_load_3d_pair(q_tiles + part * L::kTileBytes + c * L::kBoxBytes, &tm_q, cluster_addr(q_full, 0), c * 64,
+                             row0, 2 * head + part);
+      } else {
+        mbar_arrive_expect_tx(q_full, 2 * L::kTileBytes);
+        for (int part = 0; part < 2; ++part)
+          for (int c = 0; c < HD / 64; ++c)
+            tma_load_3d(q_tiles + part * L::kTileBytes + c * L::kBoxBytes, &tm_q, q_full, c * 64, row0,
+                        2 * head + part);
+      }
       bool ok = true;
       int issued = 0;
       for (int ct = 0; ct < n_ct; ++ct) {
-        const int st = ct % kLseStages;
-        ok = mbar_wait_bounded(&k_empty[st], ((ct / kLseStages) & 1) ^ 1, abort_flag);
+        const int st = ct % kStages;
+        ok = mbar_wait_bounded(&k_empty[st], ((ct / kStages) & 1) ^ 1, abort_flag);
         if (!ok) break;
-        mbar_arrive_expect_tx(&k_full[st], 2 * L::kTileBytes);
-        for (int part = 0; part < 2; ++part)
-          for (int c = 0; c < HD / 64; ++c)
-            tma_load_3d(k_ring + (st * 2 + part) * L::kTileBytes + c * L::kBoxBytes, &tm_k, &k_full[st], c * 64,
-                        (ct0 + ct) * kGemmTile, 2 * head + part);
+        if constexpr (kPair) {
+          // this CTA's 64 pooled keys of the tile (all dims), hi and lo: HD / 64 boxes of [64 keys][64 dims] each
+          if (leader) mbar_arrive_expect_tx(&k_full[st], 2 * 2 * L::kKPartBytes);
+          for (int part = 0; part < 2; ++part)
+            for (int c = 0; c < HD / 64; ++c)
+              tma_load_3d_pair(k_ring + (st * 2 + part) * L::kKPartBytes + c * L::kKBoxBytes, &tm_k,
+                               cluster_addr(&k_full[st], 0), c * 64,
+                               (ct0 + ct) * kGemmTile + static_cast<int>(rank) * (kGemmTile / 2), 2 * head + part);
+        } else {
+          mbar_arrive_expect_tx(&k_full[st], 2 * L::kTileBytes);
+          for (int part = 0; part < 2; ++part)
+            for (int c = 0; c < HD / 64; ++c)
+              tma_load_3d(k_ring + (st * 2 + part) * L::kTileBytes + c * L::kBoxBytes, &tm_k, &k_full[st], c * 64,
+                          (ct0 + ct) * kGemmTile, 2 * head + part);
+        }
         ++issued;
       }
       if (!ok) {
-        mbar_wait_bounded(q_full, 0, abort_flag + 1);
-        for (int ct = issued > kLseStages ? issued - kLseStages : 0; ct < issued; ++ct)
-          mbar_wait_bounded(&k_full[ct % kLseStages], (ct / kLseStages) & 1, abort_flag + 1);
+        // drain: the copies already issued must land before the CTA may exit
+        if (!kPair || leader) {
+          mbar_wait_bounded(q_full, 0, abort_flag + 1);
+          for (int ct = issued > kStages ? issued - kStages : 0; ct < issued; ++ct)
+            mbar_wait_bounded(&k_full[ct % kStages], (ct / kStages) & 1, abort_flag + 1);
+        } else {
+          // the other CTA of a pair has no barrier of its own for its copies (they count on the leader's):
+          // it gives them a millisecond, a thousand times what a copy from L2 or HBM takes
+          const long long t0 = clock64();
+          while (clock64() - t0 < 2000000LL) {
+          }
+        }
       }
     }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(128, 128, 0, 0);
+  } else if (warp == 1 || warp == kLseIssuerB) {
+    // Two issuing threads, one for the even column tiles and one for the odd ones: the pipe's issue queue is
+    // shallow, so the barrier waits and commits of one thread are idle gaps in its stream of MMAs, which the
+    // other thread's stream fills.
+    const int par = warp == 1 ? 0 : 1;
+    if (lane == 0 && leader) {
+      // pairs: one instruction covers the 256 pooled query rows of both CTAs; the descriptors name the same
+      // offsets in the shared memory of both
+      constexpr uint32_t idesc = umma_idesc_bf16(kPair ? 2 * kGemmTile : kGemmTile, kGemmTile, 0, 0);
       const uint64_t q_hi = umma_desc_sw128(smem_u32(q_tiles), 16, 1024);
       const uint64_t q_lo = q_hi + (L::kTileBytes >> 4);
       const uint64_t k_desc0 = umma_desc_sw128(smem_u32(k_ring), 16, 1024);
+      auto mma = [&](uint32_t d, uint64_t a, uint64_t b, uint32_t acc) {
+        if constexpr (kPair) umma_ss_pair(d, a, b, idesc, acc); else umma_ss(d, a, b, idesc, acc);
+      };
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag);
-      for (int ct = 0; ct < n_ct && ok; ++ct) {
-        const int st = ct % kLseStages, b = ct & 1;
-        ok = mbar_wait_bounded(&k_full[st], (ct / kLseStages) & 1, abort_flag);
+      for (int ct = par; ct < n_ct && ok; ct += 2) {
+        const int st = ct % kStages, b = ct % kLseBufs;
+        ok = mbar_wait_bounded(&k_full[st], (ct / kStages) & 1, abort_flag);
         if (!ok) break;
-        ok = mbar_wait_bounded(&s_empty[b], ((ct >> 1) & 1) ^ 1, abort_flag);  // passes at once the first time
+        ok = mbar_wait_bounded(&s_empty[b], ((ct / kLseBufs) & 1) ^ 1, abort_flag);  // passes at once the first time
         if (!ok) break;
         tc_fence_after_sync();
-        const uint64_t k_hi = k_desc0 + static_cast<uint64_t>(st * 2) * (L::kTileBytes >> 4);
-        const uint64_t k_lo = k_hi + (L::kTileBytes >> 4);
+        const uint64_t k_hi = k_desc0 + static_cast<uint64_t>(st * 2) * (L::kKPartBytes >> 4);
+        const uint64_t k_lo = k_hi + (L::kKPartBytes >> 4);
         const uint32_t d_tmem = tmem_base + b * 128;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint64_t off = (ks / 4) * (L::kBoxBytes >> 4) + (ks % 4) * 2;
-          umma_ss(d_tmem, q_hi + off, k_hi + off, idesc, ks > 0);
-          umma_ss(d_tmem, q_hi + off, k_lo + off, idesc, 1);
-          umma_ss(d_tmem, q_lo + off, k_hi + off, idesc, 1);
+          const uint64_t q_off = (ks / 4) * (L::kBoxBytes >> 4) + (ks % 4) * 2;
+          const uint64_t k_off = (ks / 4) * (L::kKBoxBytes >> 4) + (ks % 4) * 2;
+          mma(d_tmem, q_hi + q_off, k_hi + k_off, ks > 0);
+          mma(d_tmem, q_hi + q_off, k_lo + k_off, 1);
+          mma(d_tmem, q_lo + q_off, k_hi + k_off, 1);
         }
-        umma_commit(&k_empty[st]);
-        umma_commit(&s_full[b]);
+        if constexpr (kPair) {
+          umma_commit_pair(smem_u32(&k_empty[st]));
+          umma_commit_pair(cluster_addr(&k_empty[st], 1));
+          umma_commit_pair(smem_u32(&s_full[b]));
+          umma_commit_pair(cluster_addr(&s_full[b], 1));
+        } else {
+          umma_commit(&k_empty[st]);
+          umma_commit(&s_full[b]);
+        }
       }
       if (!ok) {
-        umma_commit(mma_drain);
-        mbar_wait_bounded(mma_drain, 0, abort_flag + 1);
+        // give-up path: let the MMAs already issued finish before TMEM is freed
+        if constexpr (kPair) umma_commit_pair(smem_u32(&mma_drain[par])); else umma_commit(&mma_drain[par]);
+        mbar_wait_bounded(&mma_drain[par], 0, abort_flag + 1);
       }
     }
   } else {
@@ -350,8 +439,8 @@ __global__ void __launch_bounds__(kLseThreads, 1)
     float* __restrict__ out_row = lse + (static_cast<size_t>(head) * s.nq + (row < s.nq ? row : 0)) * s.lse_stride;
     bool ok = true;
     for (int ct = 0; ct < n_ct; ++ct) {
-      const int b = ct & 1;
-      ok = mbar_wait_bounded(&s_full[b], (ct >> 1) & 1, abort_flag);
+      const int b = ct % kLseBufs;
+      ok = mbar_wait_bounded(&s_full[b], (ct / kLseBufs) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
       // both 32-column groups of this warp are requested before either is used
@@ -359,6 +448,12 @@ __global__ void __launch_bounds__(kLseThreads, 1)
       tmem_ld32(tmem_base + lane_sel + b * 128 + (2 * half) * 32, r[0]);
       tmem_ld32(tmem_base + lane_sel + b * 128 + (2 * half + 1) * 32, r[1]);
       tmem_wait_ld();
+      // the logits are in registers: the buffer can take the tile after the next one while they are reduced
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if (kPair && !leader) mbar_arrive_cluster(cluster_addr(&s_empty[b], 0)); else mbar_arrive(&s_empty[b]);
+      }
 #pragma unroll
       for (int gg = 0; gg < 2; ++gg) {
         const int g = 2 * half + gg;
@@ -387,19 +482,21 @@ __global__ void __launch_bounds__(kLseThreads, 1)
                 make_float4(res[4 * q4], res[4 * q4 + 1], res[4 * q4 + 2], res[4 * q4 + 3]);
         }
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[b]);
     }
   }
 
+  // pairs: a cluster-wide barrier, so that neither CTA frees its tensor memory or leaves while the other one
+  // may still signal its barriers or have an MMA running on it
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (kPair) cluster_sync_all(); else __syncthreads();
   if (abort_flag[0] != 0 && threadIdx.x == 0 && status) atomicExch(status, DFS_STATUS_WAIT_TIMEOUT);
+  if constexpr (kPair) {
+    if (misaligned && threadIdx.x == 0 && status) atomicExch(status, DFS_STATUS_BAD_SMEM_ALIGNMENT);
+  }
   if (warp == 1) {
     __syncwarp();
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 256);
+    if constexpr (kPair) tmem_dealloc_pair(tmem_base, 128 * kLseBufs); else tmem_dealloc(tmem_base, 128 * kLseBufs);
   }
 }
 
@@ -517,23 +614,54 @@ int launch_pool(const void* q, const void* k, __nv_bfloat16* qm, __nv_bfloat16* 
   return static_cast<int>(cudaGetLastError());
 }
 
+// Whether the logits kernel runs as CTA pairs (default) or as single CTAs.
+bool score_pairs_enabled() {
+  static const int flag = [] {
+    const char* e = getenv("DFSATTN_SCORE_PAIRS");
+    return e == nullptr ? 1 : (e[0] != '0');
+  }();
+  return flag != 0;
+}
+
 template <int HD, int TPB>
 int launch_lse(const __nv_bfloat16* qm, const __nv_bfloat16* km, float* lse, const ScoreShape& s, float scale_log2,
                int32_t* status, cudaStream_t stream) {
-  using L = LseSmem<HD>;
+  const int q_tiles = s.nq_pad / kGemmTile;
+  const bool pairs = q_tiles >= 2 && score_pairs_enabled();
   CUtensorMap mq, mk;
   int rc = dfs_make_bf16_tile_map(&mq, qm, 2 * s.heads, s.nq_pad, HD);
-  if (rc == 0) rc = dfs_make_bf16_tile_map(&mk, km, 2 * s.heads, s.nk_pad, HD);
+  if (rc == 0) rc = dfs_make_bf16_tile_map(&mk, km, 2 * s.heads, s.nk_pad, HD, pairs ? 64 : 128);
   if (rc != 0) return rc;
-  DFS_CUDA_CHECK(
-      cudaFuncSetAttribute(tile_lse_kernel<HD, TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
   // at least ~4 CTAs per SM's worth of work items: split the key tiles when heads x query tiles are few
-  const int ctas = (s.nq_pad / kGemmTile) * s.heads, ct_total = s.nk_pad / kGemmTile;
+  const int ctas = q_tiles * s.heads, ct_total = s.nk_pad / kGemmTile;
   int splits = (4 * 148 + ctas - 1) / ctas;
   splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
   if (splits > ct_total) splits = ct_total;
-  dim3 grid(s.nq_pad / kGemmTile, s.heads, splits);
-  tile_lse_kernel<HD, TPB><<<grid, kLseThreads, L::kTotal, stream>>>(mq, mk, lse, s, scale_log2, status);
+  if (!pairs) {
+    using L = LseSmem<HD, false>;
+    DFS_CUDA_CHECK(cudaFuncSetAttribute(tile_lse_kernel<HD, TPB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        L::kTotal));
+    dim3 grid(q_tiles, s.heads, splits);
+    tile_lse_kernel<HD, TPB, false><<<grid, kLseThreads, L::kTotal, stream>>>(mq, mk, lse, s, scale_log2, status);
+    return static_cast<int>(cudaGetLastError());
+  }
+  using L = LseSmem<HD, true>;
+  auto kernel = tile_lse_kernel<HD, TPB, true>;
+  DFS_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>((q_tiles + 1) / 2 * 2), static_cast<unsigned>(s.heads),
+                     static_cast<unsigned>(splits));
+  cfg.blockDim = dim3(kLseThreads, 1, 1);
+  cfg.dynamicSmemBytes = L::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  DFS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, mq, mk, lse, s, scale_log2, status));
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -233,6 +233,47 @@ def test_block_scores_rows_around_1024_key_blocks(ops, blocks):
     ops.check_status("cuda")
 
 
+_PAIR_SHAPES = [(2, 1024, 128, 16), (3, 128 * 9 + 57, 128, 16), (1, 128 * 33, 64, 32), (2, 128 * 17 + 5, 64, 64)]
+
+
+def test_block_scores_pairs_equal_single_ctas(ops, tmp_path):
+    """The logits kernel as CTA pairs (default: two CTAs share every pooled-K tile, 256 query rows per MMA)
+    against its single-CTA form, which a child process runs with DFSATTN_SCORE_PAIRS=0 (the switch is read
+    once per process): same bits.  Shapes with even and odd numbers of pooled query tiles, both head widths,
+    every pooled-tile size."""
+    import os
+    import subprocess
+    import sys
+    assert os.environ.get("DFSATTN_SCORE_PAIRS", "1") != "0", "this test needs the default (pairs on)"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import sys, torch\n"
+        f"sys.path.insert(0, {root!r})\n"
+        "from dfsattn_b200 import ops\n"
+        f"shapes = {_PAIR_SHAPES!r}\n"
+        "outs = []\n"
+        "for heads, L, D, tile in shapes:\n"
+        "    g = torch.Generator(device='cuda').manual_seed(L)\n"
+        "    q = torch.randn(heads, L, D, generator=g, device='cuda').bfloat16()\n"
+        "    k = torch.randn(heads, L, D, generator=g, device='cuda').bfloat16()\n"
+        "    outs.append(ops.block_scores(q, k, L, True, tile=tile).cpu())\n"
+        "torch.cuda.synchronize(); ops.check_status('cuda')\n"
+        "torch.save(outs, sys.argv[1])\n")
+    path = str(tmp_path / "single.pt")
+    res = subprocess.run([sys.executable, "-c", code, path], capture_output=True, text=True,
+                         env=dict(os.environ, DFSATTN_SCORE_PAIRS="0"), timeout=600)
+    assert res.returncode == 0, res.stderr[-3000:]
+    single = torch.load(path)
+    for (heads, L, D, tile), ref in zip(_PAIR_SHAPES, single):
+        g = torch.Generator(device="cuda").manual_seed(L)
+        q = torch.randn(heads, L, D, generator=g, device="cuda").bfloat16()
+        k = torch.randn(heads, L, D, generator=g, device="cuda").bfloat16()
+        got = ops.block_scores(q, k, L, True, tile=tile).cpu()
+        assert torch.equal(got, ref), (heads, L, D, tile, float((got - ref).abs().max()))
+    torch.cuda.synchronize()
+    ops.check_status("cuda")
+
+
 def test_block_scores_rejects_bad_shapes(ops):
     x = torch.zeros(1, 256, 128, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(ValueError):
