@@ -17,9 +17,10 @@
  *  - `stream` is a cudaStream_t passed as void*.  No call synchronises and none
  *    allocates device memory.  State kept between calls: host-side lookups that
  *    are made once (the driver's tensor-map encoder, the per-device address of
- *    the fixed scratch array of dfs_block_scores_static, the environment switch
- *    DFSATTN_DENSE_PAIRS: "0" runs dense calls on single CTAs instead of CTA
- *    pairs); nothing else.
+ *    the fixed scratch array of dfs_block_scores_static, the environment
+ *    switches DFSATTN_DENSE_PAIRS and DFSATTN_SCORE_PAIRS: "0" runs dense
+ *    attention calls, or the logits kernel of the block scoring, on single
+ *    CTAs instead of CTA pairs; same results); nothing else.
  *  - Kernels never trap: every wait inside a kernel is bounded; a kernel that
  *    gives up writes a non-zero code to `*status` (device int32, caller
  *    zero-initialised, may be NULL for kernels that have no waits).  The word
