@@ -239,6 +239,34 @@ __device__ __forceinline__ void tmem_st_16x128b_x16(uint32_t taddr, const uint32
 }
 
 // ------------------------------------------------------------------------- //
+// packed fp32x2 arithmetic and the three-input maximum (they halve the
+// instruction count of softmax-like epilogues)
+// ------------------------------------------------------------------------- //
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// ------------------------------------------------------------------------- //
 // CTA pairs: a cluster of two CTAs that run one tcgen05.mma over 256 rows
 // (cta_group::2).  Each CTA keeps its own 128 rows of the A operand and of the
 // accumulator and HALF of the B operand in its shared memory; one thread of the

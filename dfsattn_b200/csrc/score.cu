@@ -460,16 +460,14 @@ __global__ void __launch_bounds__(kLseThreads, 1)
         float res[32 / TPB];   // this thread's consecutive key blocks of the 32-column group
 #pragma unroll
         for (int grp = 0; grp < 32 / TPB; ++grp) {  // one key block = TPB consecutive pooled columns
-          float v[TPB];
-          float m = -INFINITY;
+          // max of the raw logits first, then one FMA per logit: 2^(scale * (x - max))
+          float mx = __uint_as_float(r[gg][grp * TPB]);
 #pragma unroll
-          for (int i = 0; i < TPB; ++i) {
-            v[i] = __uint_as_float(r[gg][grp * TPB + i]) * scale_log2;
-            m = fmaxf(m, v[i]);
-          }
+          for (int i = 1; i < TPB; ++i) mx = fmaxf(mx, __uint_as_float(r[gg][grp * TPB + i]));
+          const float m = mx * scale_log2;
           float sum = 0.f;
 #pragma unroll
-          for (int i = 0; i < TPB; ++i) sum += ex2_approx(v[i] - m);
+          for (int i = 0; i < TPB; ++i) sum += ex2_approx(fmaf(__uint_as_float(r[gg][grp * TPB + i]), scale_log2, -m));
           res[grp] = m + lg2_approx(sum);
         }
         // whole 16-byte vectors: a row is padded to whole column tiles (key blocks past the last one hold
