@@ -211,10 +211,11 @@ __device__ __forceinline__ void exp_pass(const uint32_t (&r)[64], uint64_t c2, u
 }
 
 // Of the 16 column groups of a score tile, how many have their exp2 evaluated by the polynomial
-// on the FMA pipe instead of the special-function unit.  Measured (same box): 2 for D = 128 (1, 3 and 4
-// are 1-2 % slower); 3 for D = 64 (2 to 5 within 2 %, 6 and 8 slower).
+// on the FMA pipe instead of the special-function unit.  Measured (same box, alternated): for D = 128, 1 and 2
+// are equal in short bursts and 1 is 0.5-0.8 % faster in a sustained loop at the power cap (none: 3-5 %
+// slower; 3 and 4: 1-2 % slower); 3 for D = 64 (2 to 5 within 2 %, 6 and 8 slower).
 #ifndef DFS_POLY_GROUPS_D128
-#define DFS_POLY_GROUPS_D128 2
+#define DFS_POLY_GROUPS_D128 1
 #endif
 #ifndef DFS_POLY_GROUPS_D64
 #define DFS_POLY_GROUPS_D64 3
