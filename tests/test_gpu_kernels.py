@@ -233,14 +233,16 @@ def test_block_scores_rows_around_1024_key_blocks(ops, blocks):
     ops.check_status("cuda")
 
 
-_PAIR_SHAPES = [(2, 1024, 128, 16), (3, 128 * 9 + 57, 128, 16), (1, 128 * 33, 64, 32), (2, 128 * 17 + 5, 64, 64)]
+# (heads, tokens, head width, tokens per pooled tile): 4, 3, 2 and 2 tiles of 128 pooled query rows (an odd count
+# leaves the last pair with one CTA whose rows are all padding), key tiles cut into several ranges per CTA
+_PAIR_SHAPES = [(2, 8192, 128, 16), (3, 128 * 40 + 57, 128, 16), (1, 128 * 33, 64, 32), (2, 128 * 70 + 5, 64, 64)]
 
 
 def test_block_scores_pairs_equal_single_ctas(ops, tmp_path):
     """The logits kernel as CTA pairs (default: two CTAs share every pooled-K tile, 256 query rows per MMA)
     against its single-CTA form, which a child process runs with DFSATTN_SCORE_PAIRS=0 (the switch is read
-    once per process): same bits.  Shapes with even and odd numbers of pooled query tiles, both head widths,
-    every pooled-tile size."""
+    once per process): same bits, and both against the oracle.  Shapes with even and odd numbers of pooled
+    query tiles, both head widths, every pooled-tile size."""
     import os
     import subprocess
     import sys
@@ -270,6 +272,8 @@ def test_block_scores_pairs_equal_single_ctas(ops, tmp_path):
         k = torch.randn(heads, L, D, generator=g, device="cuda").bfloat16()
         got = ops.block_scores(q, k, L, True, tile=tile).cpu()
         assert torch.equal(got, ref), (heads, L, D, tile, float((got - ref).abs().max()))
+        want = oracle.block_scores_wan(q.float().cpu()[None], k.float().cpu()[None], torch.arange(L), tile=tile)[0]
+        torch.testing.assert_close(got, want, rtol=2e-4, atol=1e-6)
     torch.cuda.synchronize()
     ops.check_status("cuda")
 
